@@ -571,6 +571,71 @@ int prl_weights_push(const void* src_arena, void* const* dst_arenas, int32_t n_d
                      size_t bytes, int32_t max_ctas /*0 = 2 per SM*/, prl_stream_t stream);
 int prl_weights_signal(void* const* ctrl_blocks, int32_t n_dst, uint64_t version, prl_stream_t stream);
 
+/* =======================================================================
+ * Hybrid decoders: layers that mix softmax attention (any head geometry), a state-space mixer (Mamba-2 form) and
+ * gated linear attention, with the norm on each sublayer's OUTPUT.  The reference serves whatever vLLM serves
+ * (pipelinerl/launch.py:191-247); these are the kernels the sampler engine runs for that family.  All calls work on
+ * "ragged rows": n packed token rows of several sequences, a prompt chunk beside single decoded tokens, described by
+ * per-row (row_pos, row_slot (<0 = idle), row_back = rows of the same sequence before this one in the batch) and
+ * per-segment (seg_start, seg_len, seg_pos0, seg_slot) int32 arrays on the device.  Arithmetic is fp32; `f32` selects
+ * the storage type of GEMM operands / KV cache (0 = bf16, 1 = fp32, the true-fp32 serving mode).
+ * ======================================================================= */
+/* C[M,N] = A[M,K] W[N,K]^T on the CUDA cores, any shape / stride, bf16 or fp32 operands, fp32 out; each element is
+ * summed by one thread in ascending k, so it does not depend on M or on the row's place in the batch. */
+int prl_gemm_any(const void* A, int32_t a_is_f32, int64_t lda, const void* W, int32_t w_is_f32, int64_t ldw,
+                 int64_t M, int64_t N, int64_t K, float* C, int64_t ldc, prl_stream_t stream);
+/* x = embed[token] * scale (fp32 residual) and xa = its copy in the operand type */
+int prl_embed_scale(const int32_t* tokens, const void* embed, int32_t f32, float scale, int32_t n, int32_t W,
+                    int32_t vocab, float* x, void* xa, prl_stream_t stream);
+/* y = s0*y0 (+ s1*y1);  x += y / sqrt(mean(y^2) + eps) * gain;  xa = operand-type copy of x */
+int prl_postnorm_residual(const float* y0, int64_t ld0, float s0, const float* y1 /*or NULL*/, int64_t ld1, float s1,
+                          const float* gain, float eps, int32_t n, int32_t W, float* x, void* xa, int32_t f32,
+                          prl_stream_t stream);
+/* out[i] = x[rows[i]] / rms * gain  (rows NULL = identity); the final norm in front of the head */
+int prl_rmsnorm_rows(const float* x, const int32_t* rows, const float* gain, float eps, int32_t n_out, int32_t W,
+                     void* out, int32_t f32, prl_stream_t stream);
+/* gate (silu or sigmoid of g) and optional RMS norm over groups of group_size channels, in either order */
+int prl_gate_norm(const void* o, int32_t o_f32, int64_t ldo, const float* g, int64_t ldg, const float* gain,
+                  int32_t gain_period, int32_t group_size, int32_t n, int32_t C, int32_t act_sigmoid,
+                  int32_t gate_first, int32_t norm, float eps, void* out, int32_t f32, prl_stream_t stream);
+/* out = g*sigmoid(beta*g)*(u+1), g = min(gate, limit), u = clamp(up, +-limit); gate_up = [gate | up] per row */
+int prl_glu_clamped(const float* gate_up, int64_t ld, int32_t n, int32_t F, float limit, float beta, void* out,
+                    int32_t f32, prl_stream_t stream);
+/* whole-projection RMS norm of q and of k, interleaved-pair rotary on the first `rot` channels of each head
+ * (freq[i] = base^(-2i/rot), double), q -> query buffer [n, H*dim], k / v -> paged pools */
+int prl_qk_norm_rope_cache(const float* P, int64_t ldp, int32_t off_q, int32_t off_k, int32_t off_v, int32_t n,
+                           int32_t H, int32_t G, int32_t dim, int32_t vdim, int32_t rot, const double* freq,
+                           const float* q_gain, const float* k_gain, float eps, const int32_t* row_pos,
+                           const int32_t* row_slot, const int32_t* block_table, int32_t max_blocks,
+                           int32_t page_size, void* q_out, void* k_pool, void* v_pool, int32_t f32,
+                           prl_stream_t stream);
+/* causal softmax attention over the paged pools, any dim / vdim / scale; out fp32 [n, H*vdim] */
+int prl_attn_any(const void* q, const void* k_pool, const void* v_pool, int32_t f32, const int32_t* block_table,
+                 int32_t max_blocks, int32_t page_size, const int32_t* seg_start, const int32_t* seg_len,
+                 const int32_t* seg_pos0, const int32_t* seg_slot, int32_t n_seg, int32_t max_q, int32_t H,
+                 int32_t G, int32_t dim, int32_t vdim, float scale, float* out, prl_stream_t stream);
+/* causal depthwise convolution + SiLU with a carried state of taps-1 inputs per (slot, channel); then the state shift */
+int prl_conv_silu(const float* P, int64_t ldp, int32_t off, int32_t n, int32_t ch, int32_t taps, const float* w,
+                  const float* b, const int32_t* row_slot, const int32_t* row_back, const float* state,
+                  float* out, prl_stream_t stream);
+int prl_conv_state_update(const float* P, int64_t ldp, int32_t off, int32_t ch, int32_t taps,
+                          const int32_t* seg_start, const int32_t* seg_len, const int32_t* seg_slot,
+                          int32_t n_seg, float* state, prl_stream_t stream);
+/* matrix-state recurrences S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t (csrc/lin_scan.cu); the state of a
+ * slot is prl_lin_scan_state_floats() fp32 values in a layout private to the kernels (zero = empty sequence) */
+int64_t prl_lin_scan_state_floats(int32_t heads, int32_t dk, int32_t dv);
+int prl_gla_scan(const float* P, int64_t ldp, int32_t off_q, int32_t off_k, int32_t off_v, float q_scale,
+                 const float* z, int64_t ldz, const float* z_bias, float tau, int32_t heads, int32_t dk,
+                 int32_t dv, const int32_t* seg_start, const int32_t* seg_len, const int32_t* seg_slot,
+                 int32_t n_seg, float* state, float* out, int64_t ld_out, prl_stream_t stream);
+int prl_ssd_scan(const float* P, int64_t ldp, int32_t off_dt, const float* xbc, int64_t ld_xbc,
+                 const float* dt_bias, const float* a_log, const float* skip, int32_t heads, int32_t groups,
+                 int32_t n_state, int32_t dv, const int32_t* seg_start, const int32_t* seg_len,
+                 const int32_t* seg_slot, int32_t n_seg, float* state, float* out, int64_t ld_out,
+                 prl_stream_t stream);
+/* decode step: per-slot engine state -> ragged-row metadata (seg_len = active, row_slot = slot or -1) */
+int prl_decode_rows(const uint8_t* active, int32_t B, int32_t* seg_len, int32_t* row_slot, prl_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,370 @@
+// Row kernels of the hybrid decoder family (models that mix softmax attention, state-space and gated-linear-attention
+// mixers and normalise the SUBLAYER OUTPUT instead of its input).  All of them work on a packed batch of n token rows
+// that may belong to several sequences ("ragged rows": a prompt chunk next to single decoded tokens), described by
+//   row_pos[n]   position of the token in its sequence,
+//   row_slot[n]  state / block-table slot of its sequence (< 0: idle row, nothing is read or written for it),
+//   row_back[n]  how many rows of the same sequence precede this one inside the batch.
+// Arithmetic is fp32 throughout; `T` is only the storage type of what feeds the next GEMM or the KV cache (bf16 when
+// the engine serves in bf16, fp32 in the true-fp32 mode).  Small parameter vectors (norm gains, biases, convolution
+// taps) are read as fp32 copies the engine keeps beside the weight arena.
+#include "prl_common.cuh"
+
+namespace prl {
+namespace {
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p, int64_t i);
+template <> __device__ __forceinline__ float ldf<float>(const float* p, int64_t i) { return p[i]; }
+template <> __device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p, int64_t i) { return __bfloat162float(p[i]); }
+template <typename T> __device__ __forceinline__ void stf(T* p, int64_t i, float v);
+template <> __device__ __forceinline__ void stf<float>(float* p, int64_t i, float v) { p[i] = v; }
+template <> __device__ __forceinline__ void stf<__nv_bfloat16>(__nv_bfloat16* p, int64_t i, float v) { p[i] = __float2bfloat16_rn(v); }
+
+// Sum over the block in a fixed order (warp shuffles, then the warps' partials in index order): the result for a row
+// never depends on which other rows are in the launch.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();  // red may still be read from a previous call
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int w = 0; w < nw; ++w) t += red[w];
+  return t;
+}
+
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
+
+// x = embed[token] * scale (fp32 residual) and its copy in the GEMM operand type
+template <typename T>
+__global__ void embed_scale_kernel(const int32_t* __restrict__ tokens, const T* __restrict__ embed, float scale, int W,
+                                   int vocab, float* __restrict__ x, T* __restrict__ xa) {
+  const int r = blockIdx.x;
+  int tok = tokens[r];
+  tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    const float v = ldf(embed, (int64_t)tok * W + c) * scale;
+    x[(int64_t)r * W + c] = v;
+    stf(xa, (int64_t)r * W + c, v);
+  }
+}
+
+// Post-norm residual:  y = s0*y0 + s1*y1;  x += y / sqrt(mean(y^2) + eps) * gain;  xa = T(x)
+template <typename T>
+__global__ void postnorm_residual_kernel(const float* __restrict__ y0, int64_t ld0, float s0, const float* __restrict__ y1,
+                                         int64_t ld1, float s1, const float* __restrict__ gain, float eps, int W,
+                                         float* __restrict__ x, T* __restrict__ xa) {
+  __shared__ float red[32];
+  const int r = blockIdx.x;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    float y = s0 * y0[(int64_t)r * ld0 + c];
+    if (y1) y += s1 * y1[(int64_t)r * ld1 + c];
+    ss += y * y;
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.f / sqrtf(ss / (float)W + eps);
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    float y = s0 * y0[(int64_t)r * ld0 + c];
+    if (y1) y += s1 * y1[(int64_t)r * ld1 + c];
+    const float v = x[(int64_t)r * W + c] + y * inv * gain[c];
+    x[(int64_t)r * W + c] = v;
+    stf(xa, (int64_t)r * W + c, v);
+  }
+}
+
+// out[i] = T(x[rows[i]] / rms * gain)   (rows == NULL: identity)
+template <typename T>
+__global__ void rmsnorm_rows_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows,
+                                    const float* __restrict__ gain, float eps, int W, T* __restrict__ out) {
+  __shared__ float red[32];
+  const int i = blockIdx.x;
+  const int64_t r = rows ? rows[i] : i;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    const float v = x[r * W + c];
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.f / sqrtf(ss / (float)W + eps);
+  for (int c = threadIdx.x; c < W; c += blockDim.x) stf(out, (int64_t)i * W + c, x[r * W + c] * inv * gain[c]);
+}
+
+// Gate and (group) norm between a mixer and its output projection.  One block per (row, group) of `gs` channels:
+//   gate_first:  v = o * act(g);  out = v / rms_group(v) * gain      (state-space mixer: gate, then grouped RMS norm)
+//   otherwise :  out = o / rms_group(o) * gain * act(g)              (linear attention: per-head norm, then gate)
+//   norm == 0 :  out = o * act(g)                                    (softmax attention output gate)
+// gain index = channel % gain_period (a per-head gain shared by all heads has gain_period = head size).
+template <typename T, typename TO>
+__global__ void gate_norm_kernel(const TO* __restrict__ o, int64_t ldo, const float* __restrict__ g, int64_t ldg,
+                                 const float* __restrict__ gain, int gain_period, int gs, int C, int act_sigmoid,
+                                 int gate_first, int norm, float eps, T* __restrict__ out) {
+  __shared__ float red[32];
+  const int r = blockIdx.x, c0 = blockIdx.y * gs;
+  float inv = 1.f;
+  if (norm) {
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < gs; j += blockDim.x) {
+      float v = ldf(o, (int64_t)r * ldo + c0 + j);
+      if (gate_first) {
+        const float z = g[(int64_t)r * ldg + c0 + j];
+        v *= act_sigmoid ? sigmoid_f(z) : silu_f(z);
+      }
+      ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    inv = 1.f / sqrtf(ss / (float)gs + eps);
+  }
+  for (int j = threadIdx.x; j < gs; j += blockDim.x) {
+    const int c = c0 + j;
+    const float z = g[(int64_t)r * ldg + c];
+    const float a = act_sigmoid ? sigmoid_f(z) : silu_f(z);
+    float v = ldf(o, (int64_t)r * ldo + c);
+    if (norm) v = gate_first ? (v * a) * inv * gain[c % gain_period] : v * inv * gain[c % gain_period] * a;
+    else v = v * a;
+    stf(out, (int64_t)r * C + c, v);
+  }
+}
+
+// Clamped gated feed-forward activation: g = min(gate, lim), u = clamp(up, -lim, lim), y = g*sigmoid(beta*g)*(u+1)
+template <typename T>
+__global__ void glu_clamped_kernel(const float* __restrict__ gu, int64_t ld, int F, float lim, float beta, int64_t total,
+                                   T* __restrict__ out) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int64_t r = i / F;
+  const int c = (int)(i - r * F);
+  const float g = fminf(gu[r * ld + c], lim);
+  const float u = fminf(fmaxf(gu[r * ld + F + c], -lim), lim);
+  stf(out, i, g * sigmoid_f(beta * g) * (u + 1.f));
+}
+
+// Attention front end for one row: RMS norm over the WHOLE q projection and over the whole k projection (before the
+// split into heads), rotary embedding on the first `rot` channels of every head with interleaved pairs (2i, 2i+1),
+// q to the query buffer, k / v into the paged cache.  Angles are formed in double (position * frequency) so that a
+// position in the tens of thousands keeps full fp32 accuracy in sin / cos.
+template <typename T>
+__global__ void qk_norm_rope_cache_kernel(const float* __restrict__ P, int64_t ldp, int off_q, int off_k, int off_v,
+                                          int H, int G, int dim, int vdim, int rot, const double* __restrict__ freq,
+                                          const float* __restrict__ q_gain, const float* __restrict__ k_gain, float eps,
+                                          const int32_t* __restrict__ row_pos, const int32_t* __restrict__ row_slot,
+                                          const int32_t* __restrict__ block_table, int max_blocks, int page_size,
+                                          T* __restrict__ q_out, T* __restrict__ k_pool, T* __restrict__ v_pool) {
+  extern __shared__ float cs[];  // [rot/2] cos | [rot/2] sin
+  __shared__ float red[32];
+  const int r = blockIdx.x;
+  const int slot = row_slot[r];
+  if (slot < 0) return;
+  const int pos = row_pos[r];
+  const float* q = P + (int64_t)r * ldp + off_q;
+  const float* k = P + (int64_t)r * ldp + off_k;
+  const float* v = P + (int64_t)r * ldp + off_v;
+  const int nq = H * dim, nk = G * dim, nv = G * vdim, half = rot / 2;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    double s, c;
+    sincos((double)pos * freq[i], &s, &c);
+    cs[i] = (float)c;
+    cs[half + i] = (float)s;
+  }
+  float sq = 0.f, sk = 0.f;
+  for (int i = threadIdx.x; i < nq; i += blockDim.x) sq += q[i] * q[i];
+  for (int i = threadIdx.x; i < nk; i += blockDim.x) sk += k[i] * k[i];
+  sq = block_sum(sq, red);
+  sk = block_sum(sk, red);
+  const float iq = 1.f / sqrtf(sq / (float)nq + eps), ik = 1.f / sqrtf(sk / (float)nk + eps);
+  const int page = block_table[(int64_t)slot * max_blocks + pos / page_size], within = pos % page_size;
+  for (int i = threadIdx.x; i < nq + nk; i += blockDim.x) {
+    const bool is_q = i < nq;
+    const int e = is_q ? i : i - nq;
+    const float* src = is_q ? q : k;
+    const float* gn = is_q ? q_gain : k_gain;
+    const float inv = is_q ? iq : ik;
+    const int head = e / dim, j = e % dim;
+    float val = src[e] * inv * gn[e];
+    if (j < rot) {
+      const int pe = (j & 1) ? e - 1 : e + 1;
+      const float other = src[pe] * inv * gn[pe];
+      const float c = cs[j >> 1], s = cs[half + (j >> 1)];
+      val = (j & 1) ? val * c + other * s : val * c - other * s;
+    }
+    if (is_q) stf(q_out, (int64_t)r * nq + e, val);
+    else stf(k_pool, (((int64_t)page * G + head) * page_size + within) * dim + j, val);
+  }
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    const int head = i / vdim, j = i % vdim;
+    stf(v_pool, (((int64_t)page * G + head) * page_size + within) * vdim + j, v[i]);
+  }
+}
+
+// Causal depthwise convolution + SiLU over ragged rows.  Input channel c of row r is P[r, off + c]; the tap that reaches
+// k tokens back reads row r-k if that row belongs to the same sequence inside this batch (k <= row_back[r]) and the
+// sequence's carried state otherwise.  state[slot][c][0..taps-2] holds the last taps-1 inputs, oldest first (zeros at
+// the start of a sequence).  w[c][taps-1] multiplies the current token.
+__global__ void conv_silu_kernel(const float* __restrict__ P, int64_t ldp, int off, int ch, int taps,
+                                 const float* __restrict__ w, const float* __restrict__ b,
+                                 const int32_t* __restrict__ row_slot, const int32_t* __restrict__ row_back,
+                                 const float* __restrict__ state, float* __restrict__ out) {
+  const int r = blockIdx.x;
+  const int slot = row_slot[r];
+  if (slot < 0) return;
+  const int back = row_back[r];
+  for (int c = threadIdx.x; c < ch; c += blockDim.x) {
+    float acc = b[c];
+    const float* st = state + ((int64_t)slot * ch + c) * (taps - 1);
+    for (int k = taps - 1; k >= 0; --k) {   // oldest tap first: a fixed summation order
+      const float in = (k <= back) ? P[(int64_t)(r - k) * ldp + off + c] : st[taps - 1 - (k - back)];
+      acc = fmaf(w[(int64_t)c * taps + (taps - 1 - k)], in, acc);
+    }
+    out[(int64_t)r * ch + c] = silu_f(acc);
+  }
+}
+
+// After the convolution of a batch: shift the sequence's last taps-1 inputs into its state (a segment shorter than
+// taps-1 keeps the tail of the old state).  One thread per (segment, channel) reads everything it needs before it writes.
+__global__ void conv_state_kernel(const float* __restrict__ P, int64_t ldp, int off, int ch, int taps,
+                                  const int32_t* __restrict__ seg_start, const int32_t* __restrict__ seg_len,
+                                  const int32_t* __restrict__ seg_slot, float* __restrict__ state) {
+  const int s = blockIdx.y;
+  const int len = seg_len[s];
+  if (len <= 0) return;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= ch) return;
+  const int keep = taps - 1;
+  float* st = state + ((int64_t)seg_slot[s] * ch + c) * keep;
+  const int64_t last = (int64_t)seg_start[s] + len - 1;
+  constexpr int kMaxKeep = 15;
+  float nv[kMaxKeep];
+  for (int j = 0; j < keep; ++j) {
+    const int e = keep - 1 - j;  // tokens back from the last row of the segment
+    nv[j] = (e < len) ? P[(last - e) * ldp + off + c] : st[j + len];
+  }
+  for (int j = 0; j < keep; ++j) st[j] = nv[j];
+}
+
+// Decode step: turn the engine's per-slot state into ragged-row metadata (one row per slot).
+__global__ void decode_rows_kernel(const uint8_t* __restrict__ active, int B, int32_t* __restrict__ seg_len,
+                                   int32_t* __restrict__ row_slot) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  const int a = active[b] ? 1 : 0;
+  seg_len[b] = a;
+  row_slot[b] = a ? b : -1;
+}
+
+inline int row_threads(int width) {
+  int t = ((width + 31) / 32) * 32;
+  return t < 32 ? 32 : (t > 256 ? 256 : t);
+}
+
+}  // namespace
+}  // namespace prl
+
+using namespace prl;
+typedef __nv_bfloat16 bf16;
+
+extern "C" int prl_embed_scale(const int32_t* tokens, const void* embed, int32_t f32, float scale, int32_t n, int32_t W,
+                               int32_t vocab, float* x, void* xa, prl_stream_t st) {
+  PRL_CHECK_ARG(tokens && embed && x && xa && n >= 1 && W >= 1 && vocab >= 1, "prl_embed_scale: bad argument");
+  if (f32) embed_scale_kernel<float><<<n, row_threads(W), 0, (cudaStream_t)st>>>(tokens, (const float*)embed, scale, W, vocab, x, (float*)xa);
+  else embed_scale_kernel<bf16><<<n, row_threads(W), 0, (cudaStream_t)st>>>(tokens, (const bf16*)embed, scale, W, vocab, x, (bf16*)xa);
+  PRL_LAUNCH_CHECK();
+  return PRL_OK;
+}
+
+extern "C" int prl_postnorm_residual(const float* y0, int64_t ld0, float s0, const float* y1, int64_t ld1, float s1,
+                                     const float* gain, float eps, int32_t n, int32_t W, float* x, void* xa, int32_t f32,
+                                     prl_stream_t st) {
+  PRL_CHECK_ARG(y0 && gain && x && xa && n >= 1 && W >= 1 && ld0 >= W && (!y1 || ld1 >= W), "prl_postnorm_residual: bad argument");
+  if (f32) postnorm_residual_kernel<float><<<n, row_threads(W), 0, (cudaStream_t)st>>>(y0, ld0, s0, y1, ld1, s1, gain, eps, W, x, (float*)xa);
+  else postnorm_residual_kernel<bf16><<<n, row_threads(W), 0, (cudaStream_t)st>>>(y0, ld0, s0, y1, ld1, s1, gain, eps, W, x, (bf16*)xa);
+  PRL_LAUNCH_CHECK();
+  return PRL_OK;
+}
+
+extern "C" int prl_rmsnorm_rows(const float* x, const int32_t* rows, const float* gain, float eps, int32_t n_out, int32_t W,
+                                void* out, int32_t f32, prl_stream_t st) {
+  PRL_CHECK_ARG(x && gain && out && n_out >= 1 && W >= 1, "prl_rmsnorm_rows: bad argument");
+  if (f32) rmsnorm_rows_kernel<float><<<n_out, row_threads(W), 0, (cudaStream_t)st>>>(x, rows, gain, eps, W, (float*)out);
+  else rmsnorm_rows_kernel<bf16><<<n_out, row_threads(W), 0, (cudaStream_t)st>>>(x, rows, gain, eps, W, (bf16*)out);
+  PRL_LAUNCH_CHECK();
+  return PRL_OK;
+}
+
+extern "C" int prl_gate_norm(const void* o, int32_t o_f32, int64_t ldo, const float* g, int64_t ldg, const float* gain,
+                             int32_t gain_period, int32_t group_size, int32_t n, int32_t C, int32_t act_sigmoid,
+                             int32_t gate_first, int32_t norm, float eps, void* out, int32_t f32, prl_stream_t st) {
+  PRL_CHECK_ARG(o && g && out && n >= 1 && C >= 1 && group_size >= 1 && C % group_size == 0 && ldo >= C && ldg >= C,
+                "prl_gate_norm: bad argument (C=%d group=%d)", C, group_size);
+  PRL_CHECK_ARG(!norm || (gain && gain_period >= 1), "prl_gate_norm: a norm needs its gain");
+  dim3 grid(n, C / group_size);
+  const int th = row_threads(group_size);
+  cudaStream_t s = (cudaStream_t)st;
+#define PRL_GN(T, TO) gate_norm_kernel<T, TO><<<grid, th, 0, s>>>((const TO*)o, ldo, g, ldg, gain, gain_period, group_size, C, \
+                                                                   act_sigmoid, gate_first, norm, eps, (T*)out)
+  if (f32) { if (o_f32) PRL_GN(float, float); else PRL_GN(float, bf16); }
+  else { if (o_f32) PRL_GN(bf16, float); else PRL_GN(bf16, bf16); }
+#undef PRL_GN
+  PRL_LAUNCH_CHECK();
+  return PRL_OK;
+}
+
+extern "C" int prl_glu_clamped(const float* gate_up, int64_t ld, int32_t n, int32_t F, float limit, float beta, void* out,
+                               int32_t f32, prl_stream_t st) {
+  PRL_CHECK_ARG(gate_up && out && n >= 1 && F >= 1 && ld >= 2 * (int64_t)F, "prl_glu_clamped: bad argument");
+  const int64_t total = (int64_t)n * F;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (f32) glu_clamped_kernel<float><<<blocks, 256, 0, (cudaStream_t)st>>>(gate_up, ld, F, limit, beta, total, (float*)out);
+  else glu_clamped_kernel<bf16><<<blocks, 256, 0, (cudaStream_t)st>>>(gate_up, ld, F, limit, beta, total, (bf16*)out);
+  PRL_LAUNCH_CHECK();
+  return PRL_OK;
+}
+
+extern "C" int prl_qk_norm_rope_cache(const float* P, int64_t ldp, int32_t off_q, int32_t off_k, int32_t off_v, int32_t n,
+                                      int32_t H, int32_t G, int32_t dim, int32_t vdim, int32_t rot, const double* freq,
+                                      const float* q_gain, const float* k_gain, float eps, const int32_t* row_pos,
+                                      const int32_t* row_slot, const int32_t* block_table, int32_t max_blocks,
+                                      int32_t page_size, void* q_out, void* k_pool, void* v_pool, int32_t f32,
+                                      prl_stream_t st) {
+  PRL_CHECK_ARG(P && q_gain && k_gain && row_pos && row_slot && block_table && q_out && k_pool && v_pool,
+                "prl_qk_norm_rope_cache: NULL argument");
+  PRL_CHECK_ARG(n >= 1 && H >= 1 && G >= 1 && dim >= 1 && vdim >= 1 && rot >= 0 && rot <= dim && rot % 2 == 0 &&
+                (rot == 0 || freq) && page_size >= 1 && max_blocks >= 1,
+                "prl_qk_norm_rope_cache: bad shape (H=%d G=%d dim=%d vdim=%d rot=%d)", H, G, dim, vdim, rot);
+  const size_t smem = (size_t)rot * sizeof(float);
+  cudaStream_t s = (cudaStream_t)st;
+  if (f32) qk_norm_rope_cache_kernel<float><<<n, 256, smem, s>>>(P, ldp, off_q, off_k, off_v, H, G, dim, vdim, rot, freq, q_gain, k_gain, eps,
+        row_pos, row_slot, block_table, max_blocks, page_size, (float*)q_out, (float*)k_pool, (float*)v_pool);
+  else qk_norm_rope_cache_kernel<bf16><<<n, 256, smem, s>>>(P, ldp, off_q, off_k, off_v, H, G, dim, vdim, rot, freq, q_gain, k_gain, eps,
+        row_pos, row_slot, block_table, max_blocks, page_size, (bf16*)q_out, (bf16*)k_pool, (bf16*)v_pool);
+  PRL_LAUNCH_CHECK();
+  return PRL_OK;
+}
+
+extern "C" int prl_conv_silu(const float* P, int64_t ldp, int32_t off, int32_t n, int32_t ch, int32_t taps, const float* w,
+                             const float* b, const int32_t* row_slot, const int32_t* row_back, const float* state,
+                             float* out, prl_stream_t st) {
+  PRL_CHECK_ARG(P && w && b && row_slot && row_back && state && out && n >= 1 && ch >= 1 && taps >= 1 && taps <= 16,
+                "prl_conv_silu: bad argument (taps=%d, at most 16)", taps);
+  conv_silu_kernel<<<n, row_threads(ch), 0, (cudaStream_t)st>>>(P, ldp, off, ch, taps, w, b, row_slot, row_back, state, out);
+  PRL_LAUNCH_CHECK();
+  return PRL_OK;
+}
+
+extern "C" int prl_conv_state_update(const float* P, int64_t ldp, int32_t off, int32_t ch, int32_t taps,
+                                     const int32_t* seg_start, const int32_t* seg_len, const int32_t* seg_slot,
+                                     int32_t n_seg, float* state, prl_stream_t st) {
+  PRL_CHECK_ARG(P && seg_start && seg_len && seg_slot && state && ch >= 1 && taps >= 1 && taps <= 16 && n_seg >= 1,
+                "prl_conv_state_update: bad argument");
+  if (taps == 1) return PRL_OK;
+  dim3 grid((ch + 127) / 128, n_seg);
+  conv_state_kernel<<<grid, 128, 0, (cudaStream_t)st>>>(P, ldp, off, ch, taps, seg_start, seg_len, seg_slot, state);
+  PRL_LAUNCH_CHECK();
+  return PRL_OK;
+}
+
+extern "C" int prl_decode_rows(const uint8_t* active, int32_t B, int32_t* seg_len, int32_t* row_slot, prl_stream_t st) {
+  PRL_CHECK_ARG(active && seg_len && row_slot && B >= 1, "prl_decode_rows: bad argument");
+  decode_rows_kernel<<<(B + 127) / 128, 128, 0, (cudaStream_t)st>>>(active, B, seg_len, row_slot);
+  PRL_LAUNCH_CHECK();
+  return PRL_OK;
+}

@@ -121,7 +121,9 @@ class ArenaLayout:
     def build(cfg: ModelConfig, align: int = 64) -> "ArenaLayout":
         lay = ArenaLayout(cfg)
         at = 0
-        for name, shape in fused_shapes(cfg):
+        # a model family other than Qwen2 describes its own fused tensors (cfg.fused_shapes) and checkpoint names
+        shapes = cfg.fused_shapes() if hasattr(cfg, "fused_shapes") else fused_shapes(cfg)
+        for name, shape in shapes:
             lay.offsets[name] = at
             lay.shapes[name] = shape
             at = (at + _numel(shape) + align - 1) // align * align  # 128-byte aligned tensors (TMA needs 16)
@@ -131,6 +133,8 @@ class ArenaLayout:
     # HF name -> (fused name, row start, row count)
     def hf_slices(self) -> dict[str, tuple[str, int, int]]:
         c = self.cfg
+        if hasattr(c, "checkpoint_slices"):
+            return c.checkpoint_slices()
         m: dict[str, tuple[str, int, int]] = {}
         for l in range(c.num_layers):
             hp, fp = f"model.layers.{l}.", f"layers.{l}."
@@ -180,7 +184,9 @@ class ParamArena:
         g = torch.Generator(device=self.data.device).manual_seed(seed)
         for name in self.names():
             v = self.view(name)
-            if name.endswith("layernorm.weight") or name == "norm.weight":
+            if hasattr(self.cfg, "init_param"):
+                self.cfg.init_param(name, v, g)
+            elif name.endswith("layernorm.weight") or name == "norm.weight":
                 v.fill_(1.0)
             elif name.endswith(".bias") or name.endswith("_lo"):
                 v.zero_()
@@ -202,7 +208,7 @@ class ParamArena:
                 raise KeyError(f"unexpected parameter {hf_name}")
             fused, r0, rn = slices[hf_name]
             dst = self.view(fused)[r0:r0 + rn]
-            if self.cfg.fp32_head and hf_name == "lm_head.weight":
+            if getattr(self.cfg, "fp32_head", False) and hf_name == "lm_head.weight":
                 hi = t.to(torch.bfloat16)
                 dst.copy_(hi)
                 self.view("lm_head.weight_lo").copy_((t.float() - hi.float()).to(torch.bfloat16))
@@ -210,7 +216,7 @@ class ParamArena:
                 dst.copy_(t.to(self.data.dtype))
             seen.add(hf_name)
         missing = set(slices) - seen
-        if missing == {"lm_head.weight"}:  # tied embeddings
+        if missing == {"lm_head.weight"} and "embed_tokens.weight" in self.layout.offsets:  # tied embeddings
             self.view("lm_head.weight").copy_(self.view("embed_tokens.weight"))
         elif missing:
             raise KeyError(f"missing parameters: {sorted(missing)[:4]} ...")
