@@ -216,13 +216,17 @@ class EngineCore:
             key = self.arena.data.data_ptr()
             g = self._graphs.get(key)
             if g is None:
-                self._step_kernels()  # warm-up outside capture (sets kernel attributes)
+                # The first step on a parameter buffer runs eagerly (which also sets the kernels' attributes), then the
+                # same enqueue is captured for every later step.  Capture executes nothing, and the eager run is NOT
+                # followed by a replay: a model with recurrent state must see each token exactly once.
+                self._step_kernels()
                 torch.cuda.current_stream().synchronize()
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g):
                     self._step_kernels()
                 self._graphs[key] = g
-            g.replay()
+            else:
+                g.replay()
         else:
             self._step_kernels()
         self._sample_and_advance()

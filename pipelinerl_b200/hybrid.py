@@ -351,7 +351,7 @@ class HybridEngine(EngineCore):
         """out[n, N] (fp32) = src[n, K] @ W[N, K]^T.  bf16 with TMA-expressible sizes: the tcgen05 kernels (weight-
         streaming swap-AB for n <= 128 rows, persistent CTA-pair kernel above); otherwise the CUDA-core kernel."""
         lib, st, wp = self.lib, self._st, self.arena.ptr(w_name)
-        if self.f32 or self.force_plain_gemm or K % 8 or K < 16:
+        if self.f32 or self.force_plain_gemm or K % 8 or K < 64:
             _lib.check(lib.prl_gemm_any(src.data_ptr(), int(self.f32), K, wp, int(self.f32), K, n, N, K,
                                         out.data_ptr(), N, st))
         elif n <= 128:
