@@ -624,10 +624,12 @@ int prl_conv_state_update(const float* P, int64_t ldp, int32_t off, int32_t ch, 
 /* matrix-state recurrences S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t (csrc/lin_scan.cu); the state of a
  * slot is prl_lin_scan_state_floats() fp32 values in a layout private to the kernels (zero = empty sequence) */
 int64_t prl_lin_scan_state_floats(int32_t heads, int32_t dk, int32_t dv);
+/* GLA decay in place: z[r, c] <- exp(logsigmoid(z[r, c] + bias[c]) / tau) = sigmoid(z + bias)^(1/tau) */
+int prl_gla_decay(float* z, int64_t ldz, const float* bias, float tau, int32_t n, int32_t C, prl_stream_t stream);
 int prl_gla_scan(const float* P, int64_t ldp, int32_t off_q, int32_t off_k, int32_t off_v, float q_scale,
-                 const float* z, int64_t ldz, const float* z_bias, float tau, int32_t heads, int32_t dk,
-                 int32_t dv, const int32_t* seg_start, const int32_t* seg_len, const int32_t* seg_slot,
-                 int32_t n_seg, float* state, float* out, int64_t ld_out, prl_stream_t stream);
+                 const float* decay, int64_t ld_decay, int32_t heads, int32_t dk, int32_t dv,
+                 const int32_t* seg_start, const int32_t* seg_len, const int32_t* seg_slot, int32_t n_seg,
+                 float* state, float* out, int64_t ld_out, prl_stream_t stream);
 int prl_ssd_scan(const float* P, int64_t ldp, int32_t off_dt, const float* xbc, int64_t ld_xbc,
                  const float* dt_bias, const float* a_log, const float* skip, int32_t heads, int32_t groups,
                  int32_t n_state, int32_t dv, const int32_t* seg_start, const int32_t* seg_len,

@@ -267,9 +267,10 @@ _SIGNATURES = {
     "prl_conv_state_update": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,
                                         C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),
     "prl_lin_scan_state_floats": (C.c_int64, [C.c_int32, C.c_int32, C.c_int32]),
+    "prl_gla_decay": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_float, C.c_int32, C.c_int32, C.c_void_p]),
     "prl_gla_scan": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_float, C.c_void_p, C.c_int64,
-                               C.c_void_p, C.c_float, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p,
-                               C.c_int32, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
+                               C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p,
+                               C.c_void_p, C.c_int64, C.c_void_p]),
     "prl_ssd_scan": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p,
                                C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
                                C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),

@@ -4,143 +4,282 @@
 //     o_t = S_t^T q_t  (+ skip * v_t)
 //
 // Two front ends feed the same recurrence:
-//   GATED  gated linear attention: q, k, v are columns of the projection buffer, q is scaled, and the decay is a
-//          vector per key channel, a = sigmoid(z + bias)^(1/tau), formed as exp(logsigmoid(z + bias) / tau);
+//   GATED  gated linear attention: q, k, v are columns of the projection buffer, the decay a_t is a vector per key
+//          channel, a = sigmoid(z + bias)^(1/tau), formed beforehand by prl_gla_decay as exp(logsigmoid(z + bias) / tau),
+//          and the output is scaled by q_scale;
 //   SSD    state-space duality (Mamba-2): v = x (convolved), k = dt * B, q = C, the decay is one scalar per head,
 //          a = exp(-exp(A_log) * dt) with dt = softplus(dt_raw + dt_bias), and skip = D.
 // Everything that enters the recurrence is fp32.
 //
-// Work split: grid (value tiles of 32 columns, heads, segments), 256 threads per CTA.  Thread t owns value column
-// t / 8 of the tile and the key channels d = t % 8, t % 8 + 8, ... (R of them, in registers); the 8 partial dot
-// products of a column are summed with three shuffles.  A CTA walks its segment token by token (kChunk tokens staged
-// in shared memory at a time), so prefill of a chunk and a single decoded token are the same code: a decode step is a
-// segment of length 1 whose cost is the state's round trip through HBM.  The state is stored in the order the threads
-// hold it, [slot][head][tile][r][thread], so that round trip is fully coalesced; its layout is private to this file.
-// The result for a token depends only on the tokens before it in its own sequence: chunk borders, batch composition
-// and slot numbers cannot change a bit of it.
+// Work split: grid (value tiles, heads, segments), 64 threads per CTA.  Thread t owns VC adjacent value columns
+// (t / 8) * VC .. and the key channels d = (t % 8) * R .. + R - 1, i.e. R x VC state elements in registers; a, k, q
+// of a token are read from shared memory once per key channel and reused for the VC columns (128-bit loads from a
+// padded, conflict-free layout); the 8 partial dot products of a column are summed with three shuffles.  VC (4, 2
+// or 1) is picked per launch so that the grid fills the SMs: many sequences take wide tiles (a, k, q staged once per
+// 32 columns), a single long prompt takes narrow ones (four times as many CTAs).  The arithmetic per state element
+// is the same for every VC, bit for bit.  A CTA walks
+// its segment token by token; tokens are staged kChunk at a time with cp.async into a double buffer, so the loads of
+// the next chunk overlap the arithmetic of this one.  Prefill of a chunk and a single decoded token are the same
+// code: a decode step is a segment of length 1 whose cost is the state's round trip through HBM.  The state is stored
+// as [slot][head][r][column / 4][key lane][column % 4], which a warp reads as whole 128-byte lines for every VC; the layout
+// is private to this file.  The result for a token depends only on the tokens before it in its own sequence: chunk
+// borders, batch composition and slot numbers cannot change a bit of it.
 #include "prl_common.cuh"
 
 namespace prl {
 namespace {
 
-constexpr int kChunk = 8;      // tokens staged per round
-constexpr int kColsPerCta = 32;
-constexpr int kKeyLanes = 8;
+constexpr int kChunk = 8;       // tokens staged per round
+constexpr int kKeyLanes = 8;    // threads that share a value column
+constexpr int kThreads = 64;
 
 struct ScanArgs {
-  // ragged segments
   const int32_t* seg_start; const int32_t* seg_len; const int32_t* seg_slot;
-  // recurrence shape
   int heads, dk, dv;
   float* state; int64_t state_slot_stride;      // floats per slot
   float* out; int64_t ld_out;                   // [n, heads*dv] fp32
-  // GATED front end
-  const float* P; int64_t ldp; int off_q, off_k, off_v; float q_scale;
-  const float* z; int64_t ldz; const float* z_bias; float inv_tau;
-  // SSD front end
-  const float* xbc; int64_t ld_xbc; int groups; int off_dt;
+  // per-token vectors: base + row * ld + column offset (the head / group offset is added in the kernel)
+  const float* kvec; int64_t ld_k; int off_k;
+  const float* qvec; int64_t ld_q; int off_q;
+  const float* avec; int64_t ld_a;              // GATED: decay per key channel
+  const float* xval; int64_t ld_x; int off_x;   // value columns
+  float q_scale;
+  // SSD scalars
+  const float* dt_raw; int64_t ld_dt; int off_dt; int groups;
   const float* dt_bias; const float* a_log; const float* skip;
 };
 
 __device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
 __device__ __forceinline__ float logsigmoid_f(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
-template <int R, bool SSD>
-__global__ void __launch_bounds__(256) lin_scan_kernel(ScanArgs a) {
-  extern __shared__ float sm[];
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int R, int VC, bool SSD>
+__global__ void __launch_bounds__(kThreads) lin_scan_kernel(ScanArgs a) {
+  constexpr int kCols = kKeyLanes * VC;          // value columns per CTA
+  constexpr int RS = R + 4;                      // padded stride of one thread's key-channel block (conflict-free LDS.128)
+  constexpr int kVecTok = kKeyLanes * RS;        // floats per token and vector
+  constexpr int kNVec = SSD ? 2 : 3;
+  constexpr int kBuf = kChunk * (kNVec * kVecTok + kCols + 2);
+  extern __shared__ __align__(16) float sm[];
   const int seg = blockIdx.z, h = blockIdx.y, vt = blockIdx.x;
   const int len = a.seg_len[seg];
   if (len <= 0) return;
-  const int tid = threadIdx.x, dg = tid % kKeyLanes, vl = tid / kKeyLanes;
-  const int v = vt * kColsPerCta + vl;
-  const bool v_ok = v < a.dv;
-  const int dk = a.dk;
-  float* s_a = sm;                       // [kChunk][dk] decay
-  float* s_k = s_a + kChunk * dk;        // [kChunk][dk] key coefficient
-  float* s_q = s_k + kChunk * dk;        // [kChunk][dk] query coefficient
-  float* s_v = s_q + kChunk * dk;        // [kChunk][32] value column
+  const int tid = threadIdx.x, dg = tid % kKeyLanes, vg = tid / kKeyLanes;
+  const int dk = a.dk, dv = a.dv;
   const int64_t row0 = a.seg_start[seg];
-  const int n_vt = gridDim.x;
-  float* st = a.state + (int64_t)a.seg_slot[seg] * a.state_slot_stride + ((int64_t)h * n_vt + vt) * (R * 256);
-  float s[R];
+  const int nv4 = (dv + 3) / 4;                  // state layout: [head][r][column / 4][key lane][column % 4]
+  float* st = a.state + (int64_t)a.seg_slot[seg] * a.state_slot_stride + (int64_t)h * R * nv4 * 32;
+  const int col0 = vt * kCols + vg * VC;
+  float s[R][VC];
 #pragma unroll
-  for (int i = 0; i < R; ++i) s[i] = st[i * 256 + tid];
-  const int grp = SSD ? h / (a.heads / a.groups) : 0;
-  const int inner = a.heads * a.dv;
-  float skip = 0.f, neg_a = 0.f, dtb = 0.f;
-  if (SSD) { skip = a.skip[h]; neg_a = -expf(a.a_log[h]); dtb = a.dt_bias[h]; }
-
-  for (int t0 = 0; t0 < len; t0 += kChunk) {
-    const int nt = min(kChunk, len - t0);
-    __syncthreads();
-    for (int i = tid; i < nt * dk; i += 256) {
-      const int t = i / dk, d = i - t * dk;
-      const int64_t r = row0 + t0 + t;
-      if (SSD) {
-        const float dt = softplus_f(a.P[r * a.ldp + a.off_dt + h] + dtb);
-        s_a[i] = expf(neg_a * dt);
-        s_k[i] = dt * a.xbc[r * a.ld_xbc + inner + grp * dk + d];
-        s_q[i] = a.xbc[r * a.ld_xbc + inner + a.groups * dk + grp * dk + d];
-      } else {
-        const float zz = a.z[r * a.ldz + h * dk + d] + a.z_bias[h * dk + d];
-        s_a[i] = expf(logsigmoid_f(zz) * a.inv_tau);
-        s_k[i] = a.P[r * a.ldp + a.off_k + h * dk + d];
-        s_q[i] = a.P[r * a.ldp + a.off_q + h * dk + d] * a.q_scale;
-      }
-    }
-    for (int i = tid; i < nt * kColsPerCta; i += 256) {
-      const int t = i / kColsPerCta, c = i - t * kColsPerCta;
-      const int vv = vt * kColsPerCta + c;
-      const int64_t r = row0 + t0 + t;
-      float x = 0.f;
-      if (vv < a.dv) x = SSD ? a.xbc[r * a.ld_xbc + h * a.dv + vv] : a.P[r * a.ldp + a.off_v + h * a.dv + vv];
-      s_v[i] = x;
-    }
-    __syncthreads();
-    for (int t = 0; t < nt; ++t) {
-      const float xv = s_v[t * kColsPerCta + vl];
-      const float* pa = s_a + t * dk;
-      const float* pk = s_k + t * dk;
-      const float* pq = s_q + t * dk;
-      float acc = 0.f;
+  for (int i = 0; i < R; ++i) {
+    if constexpr (VC == 4) {        // col0 is a multiple of 4: the thread's four columns are one 16-byte group
+      float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (col0 < nv4 * 4) v4 = *reinterpret_cast<const float4*>(st + (((int64_t)i * nv4 + col0 / 4) * kKeyLanes + dg) * 4);
+      s[i][0] = v4.x; s[i][1] = v4.y; s[i][2] = v4.z; s[i][3] = v4.w;
+    } else {
 #pragma unroll
-      for (int i = 0; i < R; ++i) {
-        const int d = dg + kKeyLanes * i;
-        if (d < dk) {
-          s[i] = fmaf(pa[d], s[i], pk[d] * xv);
-          acc = fmaf(s[i], pq[d], acc);
-        }
+      for (int j = 0; j < VC; ++j) {
+        const int c = col0 + j;
+        s[i][j] = (c < nv4 * 4) ? st[(((int64_t)i * nv4 + c / 4) * kKeyLanes + dg) * 4 + (c & 3)] : 0.f;
       }
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-      if (dg == 0 && v_ok) a.out[(row0 + t0 + t) * a.ld_out + h * a.dv + v] = acc + skip * xv;
     }
   }
+  const int grp = SSD ? h / (a.heads / a.groups) : 0;
+  float skip = 0.f, neg_a = 0.f, dtb = 0.f;
+  if (SSD) { skip = a.skip[h]; neg_a = -expf(a.a_log[h]); dtb = a.dt_bias[h]; }
+  for (int i = tid; i < 2 * kBuf; i += kThreads) sm[i] = 0.f;   // padding slots (d >= dk, v >= dv) stay zero for good
+  __syncthreads();
+
+  const float* kbase = a.kvec + a.off_k + (SSD ? grp : h) * dk;
+  const float* qbase = a.qvec + a.off_q + (SSD ? grp : h) * dk;
+  const float* abase = SSD ? nullptr : a.avec + h * dk;
+  const float* xbase = a.xval + a.off_x + h * dv + vt * kCols;
+  const int cols_here = min(kCols, dv - vt * kCols);
+
+  auto stage = [&](int t0, float* buf) {
+    const int nt = min(kChunk, len - t0);
+    float* bk = buf;
+    float* bq = bk + kChunk * kVecTok;
+    float* ba = bq + kChunk * kVecTok;                       // GATED only
+    float* bx = buf + kChunk * kNVec * kVecTok;
+    float* bs = bx + kChunk * kCols;                         // SSD: raw dt per token
+    for (int t = 0; t < nt; ++t) {
+      const int64_t r = row0 + t0 + t;
+      for (int d = tid; d < dk; d += kThreads) {
+        const int o = t * kVecTok + (d / R) * RS + (d % R);
+        cp_async4(bk + o, kbase + r * a.ld_k + d);
+        cp_async4(bq + o, qbase + r * a.ld_q + d);
+        if (!SSD) cp_async4(ba + o, abase + r * a.ld_a + d);
+      }
+    }
+    for (int i = tid; i < nt * kCols; i += kThreads) {
+      const int t = i / kCols, c = i % kCols;
+      if (c < cols_here) cp_async4(bx + t * kCols + c, xbase + (row0 + t0 + t) * a.ld_x + c);
+    }
+    if (SSD && tid < nt) cp_async4(bs + tid, a.dt_raw + (row0 + t0 + tid) * a.ld_dt + a.off_dt + h);
+    cp_async_commit();
+  };
+
+  stage(0, sm);
+  int cur = 0;
+  for (int t0 = 0; t0 < len; t0 += kChunk, cur ^= 1) {
+    const int nt = min(kChunk, len - t0);
+    float* buf = sm + cur * kBuf;
+    if (t0 + kChunk < len) {
+      stage(t0 + kChunk, sm + (cur ^ 1) * kBuf);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const float* bk = buf;
+    const float* bq = bk + kChunk * kVecTok;
+    const float* ba = bq + kChunk * kVecTok;
+    const float* bx = buf + kChunk * kNVec * kVecTok;
+    float* bs = buf + kChunk * kNVec * kVecTok + kChunk * kCols;
+    if (SSD) {
+      if (tid < nt) {
+        const float dt = softplus_f(bs[tid] + dtb);
+        bs[tid] = dt;
+        bs[kChunk + tid] = expf(neg_a * dt);
+      }
+      __syncthreads();
+    }
+    auto token = [&](int t) {
+      float xv[VC], xin[VC], acc[VC];
 #pragma unroll
-  for (int i = 0; i < R; ++i) st[i * 256 + tid] = s[i];
+      for (int j = 0; j < VC; ++j) {
+        xv[j] = bx[t * kCols + vg * VC + j];
+        xin[j] = SSD ? xv[j] * bs[t] : xv[j];
+        acc[j] = 0.f;
+      }
+      const float dec = SSD ? bs[kChunk + t] : 0.f;
+      const float* pk = bk + t * kVecTok + dg * RS;
+      const float* pq = bq + t * kVecTok + dg * RS;
+      const float* pa = ba + t * kVecTok + dg * RS;
+      if constexpr (R % 4 == 0) {
+#pragma unroll
+        for (int i4 = 0; i4 < R / 4; ++i4) {
+          const float4 k4 = *reinterpret_cast<const float4*>(pk + 4 * i4);
+          const float4 q4 = *reinterpret_cast<const float4*>(pq + 4 * i4);
+          float4 a4 = make_float4(dec, dec, dec, dec);
+          if (!SSD) a4 = *reinterpret_cast<const float4*>(pa + 4 * i4);
+          const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w}, aa[4] = {a4.x, a4.y, a4.z, a4.w};
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+#pragma unroll
+            for (int j = 0; j < VC; ++j) {
+              s[4 * i4 + u][j] = fmaf(aa[u], s[4 * i4 + u][j], kk[u] * xin[j]);
+              acc[j] = fmaf(s[4 * i4 + u][j], qq[u], acc[j]);
+            }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+          const float kk = pk[i], qq = pq[i], aa = SSD ? dec : pa[i];
+#pragma unroll
+          for (int j = 0; j < VC; ++j) {
+            s[i][j] = fmaf(aa, s[i][j], kk * xin[j]);
+            acc[j] = fmaf(s[i][j], qq, acc[j]);
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < VC; ++j) {
+        acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], 1);
+        acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], 2);
+        acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], 4);
+      }
+      if (dg == 0) {
+        float* o = a.out + (row0 + t0 + t) * a.ld_out + h * dv + vt * kCols + vg * VC;
+#pragma unroll
+        for (int j = 0; j < VC; ++j)
+          if (vg * VC + j < cols_here) o[j] = SSD ? acc[j] + skip * xv[j] : acc[j] * a.q_scale;
+      }
+    };
+    if (nt == kChunk) {   // a full chunk: unrolled, so that one token's shuffles and store overlap the next token's loads
+#pragma unroll
+      for (int t = 0; t < kChunk; ++t) token(t);
+    } else {
+      for (int t = 0; t < nt; ++t) token(t);
+    }
+    __syncthreads();     // the buffer is free for the chunk after next
+  }
+#pragma unroll
+  for (int i = 0; i < R; ++i) {
+    if constexpr (VC == 4) {
+      if (col0 < nv4 * 4)
+        *reinterpret_cast<float4*>(st + (((int64_t)i * nv4 + col0 / 4) * kKeyLanes + dg) * 4) =
+            make_float4(s[i][0], s[i][1], s[i][2], s[i][3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < VC; ++j) {
+        const int c = col0 + j;
+        if (c < nv4 * 4) st[(((int64_t)i * nv4 + c / 4) * kKeyLanes + dg) * 4 + (c & 3)] = s[i][j];
+      }
+    }
+  }
 }
 
-template <bool SSD>
-int launch_scan(const ScanArgs& a, int n_seg, cudaStream_t st) {
-  const int r_need = (a.dk + kKeyLanes - 1) / kKeyLanes;
-  dim3 grid((a.dv + kColsPerCta - 1) / kColsPerCta, a.heads, n_seg);
-  const size_t smem = (size_t)kChunk * (3 * a.dk + kColsPerCta) * sizeof(float);
-  if (r_need <= 1) lin_scan_kernel<1, SSD><<<grid, 256, smem, st>>>(a);
-  else if (r_need <= 2) lin_scan_kernel<2, SSD><<<grid, 256, smem, st>>>(a);
-  else if (r_need <= 4) lin_scan_kernel<4, SSD><<<grid, 256, smem, st>>>(a);
-  else if (r_need <= 8) lin_scan_kernel<8, SSD><<<grid, 256, smem, st>>>(a);
-  else if (r_need <= 16) lin_scan_kernel<16, SSD><<<grid, 256, smem, st>>>(a);
-  else lin_scan_kernel<32, SSD><<<grid, 256, smem, st>>>(a);
-  PRL_LAUNCH_CHECK();
-  return PRL_OK;
-}
-
-int scan_r(int dk) {
+// R = key channels per thread (dk <= 8 R, a power of two)
+int plan_r(int dk) {
   const int need = (dk + kKeyLanes - 1) / kKeyLanes;
   int r = 1;
   while (r < need) r *= 2;
   return r;
+}
+
+template <int R, int VC, bool SSD>
+int launch_one(const ScanArgs& a, int n_seg, cudaStream_t st) {
+  constexpr int kCols = kKeyLanes * VC;
+  constexpr int kNVec = SSD ? 2 : 3;
+  const size_t smem = 2 * (size_t)kChunk * (kNVec * kKeyLanes * (R + 4) + kCols + 2) * sizeof(float);
+  static SmemAttr attr = {};
+  if (smem > 48 * 1024) PRL_CUDA(ensure_smem(lin_scan_kernel<R, VC, SSD>, (int)smem, attr));
+  dim3 grid((a.dv + kCols - 1) / kCols, a.heads, n_seg);
+  lin_scan_kernel<R, VC, SSD><<<grid, kThreads, smem, st>>>(a);
+  PRL_LAUNCH_CHECK();
+  return PRL_OK;
+}
+
+// value columns per thread: the widest tile that still gives two CTAs per SM
+template <int R, bool SSD>
+int launch_r(const ScanArgs& a, int n_seg, cudaStream_t st) {
+  const int64_t want = 2 * (int64_t)num_sms();
+  auto ctas = [&](int vc) { return (int64_t)((a.dv + 8 * vc - 1) / (8 * vc)) * a.heads * n_seg; };
+  if (R <= 16 && ctas(4) >= want) return launch_one<R, (R <= 16 ? 4 : 2), SSD>(a, n_seg, st);
+  if (ctas(2) >= want) return launch_one<R, 2, SSD>(a, n_seg, st);
+  return launch_one<R, 1, SSD>(a, n_seg, st);
+}
+
+template <bool SSD>
+int launch_scan(const ScanArgs& a, int n_seg, cudaStream_t st) {
+  switch (plan_r(a.dk)) {
+    case 1: return launch_r<1, SSD>(a, n_seg, st);
+    case 2: return launch_r<2, SSD>(a, n_seg, st);
+    case 4: return launch_r<4, SSD>(a, n_seg, st);
+    case 8: return launch_r<8, SSD>(a, n_seg, st);
+    case 16: return launch_r<16, SSD>(a, n_seg, st);
+    default: return launch_r<32, SSD>(a, n_seg, st);
+  }
+}
+
+__global__ void gla_decay_kernel(float* __restrict__ z, int64_t ldz, const float* __restrict__ bias, float inv_tau, int C,
+                                 int64_t total) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int64_t r = i / C;
+  const int c = (int)(i - r * C);
+  float* p = z + r * ldz + c;
+  *p = expf(logsigmoid_f(*p + bias[c]) * inv_tau);
 }
 
 }  // namespace
@@ -150,24 +289,34 @@ using namespace prl;
 
 extern "C" int64_t prl_lin_scan_state_floats(int32_t heads, int32_t dk, int32_t dv) {
   if (heads < 1 || dk < 1 || dk > 256 || dv < 1) return -1;
-  const int64_t tiles = (dv + kColsPerCta - 1) / kColsPerCta;
-  return (int64_t)heads * tiles * scan_r(dk) * 256;
+  return (int64_t)heads * plan_r(dk) * ((dv + 3) / 4) * 32;
+}
+
+extern "C" int prl_gla_decay(float* z, int64_t ldz, const float* bias, float tau, int32_t n, int32_t C, prl_stream_t st) {
+  PRL_CHECK_ARG(z && bias && n >= 1 && C >= 1 && ldz >= C && tau > 0.f, "prl_gla_decay: bad argument");
+  const int64_t total = (int64_t)n * C;
+  gla_decay_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)st>>>(z, ldz, bias, 1.f / tau, C, total);
+  PRL_LAUNCH_CHECK();
+  return PRL_OK;
 }
 
 extern "C" int prl_gla_scan(const float* P, int64_t ldp, int32_t off_q, int32_t off_k, int32_t off_v, float q_scale,
-                            const float* z, int64_t ldz, const float* z_bias, float tau, int32_t heads, int32_t dk,
-                            int32_t dv, const int32_t* seg_start, const int32_t* seg_len, const int32_t* seg_slot,
-                            int32_t n_seg, float* state, float* out, int64_t ld_out, prl_stream_t st) {
-  PRL_CHECK_ARG(P && z && z_bias && seg_start && seg_len && seg_slot && state && out, "prl_gla_scan: NULL argument");
-  PRL_CHECK_ARG(heads >= 1 && dk >= 1 && dk <= 256 && dv >= 1 && n_seg >= 1 && n_seg <= 65535 && tau > 0.f,
+                            const float* decay, int64_t ld_decay, int32_t heads, int32_t dk, int32_t dv,
+                            const int32_t* seg_start, const int32_t* seg_len, const int32_t* seg_slot, int32_t n_seg,
+                            float* state, float* out, int64_t ld_out, prl_stream_t st) {
+  PRL_CHECK_ARG(P && decay && seg_start && seg_len && seg_slot && state && out, "prl_gla_scan: NULL argument");
+  PRL_CHECK_ARG(heads >= 1 && dk >= 1 && dk <= 256 && dv >= 1 && n_seg >= 1 && n_seg <= 65535,
                 "prl_gla_scan: bad shape (heads=%d dk=%d dv=%d, dk at most 256)", heads, dk, dv);
   ScanArgs a = {};
   a.seg_start = seg_start; a.seg_len = seg_len; a.seg_slot = seg_slot;
   a.heads = heads; a.dk = dk; a.dv = dv;
   a.state = state; a.state_slot_stride = prl_lin_scan_state_floats(heads, dk, dv);
   a.out = out; a.ld_out = ld_out;
-  a.P = P; a.ldp = ldp; a.off_q = off_q; a.off_k = off_k; a.off_v = off_v; a.q_scale = q_scale;
-  a.z = z; a.ldz = ldz; a.z_bias = z_bias; a.inv_tau = 1.f / tau;
+  a.kvec = P; a.ld_k = ldp; a.off_k = off_k;
+  a.qvec = P; a.ld_q = ldp; a.off_q = off_q;
+  a.avec = decay; a.ld_a = ld_decay;
+  a.xval = P; a.ld_x = ldp; a.off_x = off_v;
+  a.q_scale = q_scale;
   return launch_scan<false>(a, n_seg, (cudaStream_t)st);
 }
 
@@ -181,13 +330,17 @@ extern "C" int prl_ssd_scan(const float* P, int64_t ldp, int32_t off_dt, const f
   PRL_CHECK_ARG(heads >= 1 && groups >= 1 && heads % groups == 0 && n_state >= 1 && n_state <= 256 && dv >= 1 &&
                 n_seg >= 1 && n_seg <= 65535,
                 "prl_ssd_scan: bad shape (heads=%d groups=%d state=%d dv=%d, state at most 256)", heads, groups, n_state, dv);
+  const int inner = heads * dv;
   ScanArgs a = {};
   a.seg_start = seg_start; a.seg_len = seg_len; a.seg_slot = seg_slot;
   a.heads = heads; a.dk = n_state; a.dv = dv;
   a.state = state; a.state_slot_stride = prl_lin_scan_state_floats(heads, n_state, dv);
   a.out = out; a.ld_out = ld_out;
-  a.P = P; a.ldp = ldp; a.off_dt = off_dt;
-  a.xbc = xbc; a.ld_xbc = ld_xbc; a.groups = groups;
+  a.kvec = xbc; a.ld_k = ld_xbc; a.off_k = inner;                         // B: [groups][state] after x
+  a.qvec = xbc; a.ld_q = ld_xbc; a.off_q = inner + groups * n_state;      // C
+  a.xval = xbc; a.ld_x = ld_xbc; a.off_x = 0;
+  a.q_scale = 1.f;
+  a.dt_raw = P; a.ld_dt = ldp; a.off_dt = off_dt; a.groups = groups;
   a.dt_bias = dt_bias; a.a_log = a_log; a.skip = skip;
   return launch_scan<true>(a, n_seg, (cudaStream_t)st);
 }

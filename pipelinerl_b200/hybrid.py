@@ -281,6 +281,7 @@ class _Rows:
         self.aux = torch.zeros(n * wide_aux, **f32)             # decay logits (GLA) / convolved x, B, C (state-space)
         self.o = torch.zeros(n * wide_o, **f32)                 # raw mixer output (GLA, attention)
         self.o2 = torch.zeros(n * wide_o2, **f32)               # raw state-space output
+        self.ob = torch.zeros(n * wide_o if any(eng.tc_attn.values()) else 1, dtype=torch.bfloat16, device=d)  # tcgen05 attention out
         self.ya = torch.zeros(n * wide_o, dtype=T, device=d)    # gated / normed input of the output projection
         self.yb = torch.zeros(n * wide_o2, dtype=T, device=d)
         self.y0 = torch.zeros(n * W, **f32)
@@ -304,6 +305,7 @@ class HybridEngine(EngineCore):
         if self.op_dtype not in (torch.float32, torch.bfloat16):
             raise ValueError("the hybrid engine runs bf16 or fp32 weights")
         self.force_plain_gemm = False      # tests: route every GEMM through the CUDA-core kernel
+        self.force_plain_attn = False      # tests: the any-geometry attention kernel also where the tcgen05 ones fit
         self._rows: _Rows | None = None
         super().__init__(cfg, arena, **kw)
 
@@ -311,6 +313,7 @@ class HybridEngine(EngineCore):
     def _alloc_model(self) -> None:
         cfg, d, lib = self.cfg, self.dev, self.lib
         self.k_pool, self.v_pool, self.conv_state, self.ssd_state, self.gla_state, self.rot_freq = {}, {}, {}, {}, {}, {}
+        self.tc_attn: dict[int, bool] = {}
         for i, L in enumerate(cfg.layers):               # one cache / state per layer RUN, also where weights are shared
             if L.kind == "gla":
                 g = L.gla
@@ -318,8 +321,16 @@ class HybridEngine(EngineCore):
                 self.gla_state[i] = self.states.add(f"l{i}.gla", (n,))
             else:
                 a, s = L.attn, L.ssd
-                self.k_pool[i] = torch.zeros(self.n_pages, a.kv_heads, PAGE_SIZE, a.dim, dtype=self.op_dtype, device=d)
-                self.v_pool[i] = torch.zeros(self.n_pages, a.kv_heads, PAGE_SIZE, a.vdim, dtype=self.op_dtype, device=d)
+                if a.dim == a.vdim:    # K and V pools adjacent: [2][page][kv head][64][d], the layout of the Qwen2 engine's pool
+                    pair = torch.zeros(2, self.n_pages, a.kv_heads, PAGE_SIZE, a.dim, dtype=self.op_dtype, device=d)
+                    self.k_pool[i], self.v_pool[i] = pair[0], pair[1]
+                else:
+                    self.k_pool[i] = torch.zeros(self.n_pages, a.kv_heads, PAGE_SIZE, a.dim, dtype=self.op_dtype, device=d)
+                    self.v_pool[i] = torch.zeros(self.n_pages, a.kv_heads, PAGE_SIZE, a.vdim, dtype=self.op_dtype, device=d)
+                # head size 128 in bf16 is what the tcgen05 chunked-prefill kernel and the TMA paged-decode kernel are built
+                # for: such a layer runs the SAME attention kernels as the Qwen2 engine (with this layer's own scale)
+                self.tc_attn[i] = (not self.f32 and a.dim == 128 and a.vdim == 128
+                                   and a.heads // a.kv_heads in (1, 2, 4, 8, 16))
                 self.conv_state[i] = self.states.add(f"l{i}.conv", (s.conv_channels, max(s.conv - 1, 1)))
                 n = int(lib.prl_lin_scan_state_floats(s.heads, s.state, s.vdim))
                 self.ssd_state[i] = self.states.add(f"l{i}.ssd", (n,))
@@ -333,6 +344,13 @@ class HybridEngine(EngineCore):
                 self.vec[name] = torch.zeros(shape, dtype=torch.float32, device=d)
         self._on_arena_change()
         B = self.B
+        self.attn_splits, ws = {}, 0
+        for i, on in self.tc_attn.items():
+            if on:
+                a = cfg.layers[i].attn
+                self.attn_splits[i] = int(lib.prl_paged_attn_splits(B, a.kv_heads, self.max_seq_len))
+                ws = max(ws, int(lib.prl_paged_attn_workspace_bytes(B, a.heads, self.attn_splits[i])))
+        self.attn_ws = torch.zeros(max(ws, 16), dtype=torch.uint8, device=d)
         self._dec = _Rows(self, B)
         i32 = dict(dtype=torch.int32, device=d)
         self._dec.seg[0].copy_(torch.arange(B, **i32))
@@ -361,7 +379,7 @@ class HybridEngine(EngineCore):
 
     # ---- the layer program over n ragged rows -------------------------------------------------------------------------
     def _layers(self, R: _Rows, n: int, ns: int, max_q: int, row_pos: torch.Tensor, seg_pos0: torch.Tensor,
-                trace=None) -> None:
+                trace=None, decode: bool = False) -> None:
         cfg, lib, st, f32 = self.cfg, self.lib, self._st, int(self.f32)
         W, eps, vec = cfg.width, cfg.eps, self.vec
         seg_start, seg_len, seg_slot = R.seg[0].data_ptr(), R.seg[1].data_ptr(), R.seg[3].data_ptr()
@@ -376,9 +394,10 @@ class HybridEngine(EngineCore):
                 # decay logits z = W_a2 (W_a1 h): the bottleneck stays fp32 (A operand read from P as stored)
                 _lib.check(lib.prl_gemm_any(P + 4 * (2 * nq + 2 * nv), 1, ld, self.arena.ptr(w + "mix.a2"), f32, g.rank,
                                             n, nq, g.rank, R.aux.data_ptr(), nq, st))
-                _lib.check(lib.prl_gla_scan(P, ld, 0, nq, 2 * nq, g.dim ** -0.5, R.aux.data_ptr(), nq,
-                                            vec[w + "mix.a2.b"].data_ptr(), g.tau, g.heads, g.dim, g.vdim, seg_start,
-                                            seg_len, seg_slot, ns, self.gla_state[i].data_ptr(), R.o.data_ptr(), nv, st))
+                _lib.check(lib.prl_gla_decay(R.aux.data_ptr(), nq, vec[w + "mix.a2.b"].data_ptr(), g.tau, n, nq, st))
+                _lib.check(lib.prl_gla_scan(P, ld, 0, nq, 2 * nq, g.dim ** -0.5, R.aux.data_ptr(), nq, g.heads, g.dim, g.vdim,
+                                            seg_start, seg_len, seg_slot, ns, self.gla_state[i].data_ptr(), R.o.data_ptr(),
+                                            nv, st))
                 _lib.check(lib.prl_gate_norm(R.o.data_ptr(), 1, nv, P + 4 * (2 * nq + nv), ld, vec[w + "mix.norm"].data_ptr(),
                                              g.vdim, g.vdim, n, nv, 0, 0, 1, eps, R.ya.data_ptr(), f32, st))
                 self._mm(R.ya, nv, w + "mix.o", W, R.y0, n)
@@ -398,11 +417,26 @@ class HybridEngine(EngineCore):
                                                       R.row_slot.data_ptr(), self.block_table.data_ptr(), self.max_blocks,
                                                       PAGE_SIZE, R.q.data_ptr(), self.k_pool[i].data_ptr(),
                                                       self.v_pool[i].data_ptr(), f32, st))
-                _lib.check(lib.prl_attn_any(R.q.data_ptr(), self.k_pool[i].data_ptr(), self.v_pool[i].data_ptr(), f32,
-                                            self.block_table.data_ptr(), self.max_blocks, PAGE_SIZE, seg_start, seg_len,
-                                            seg_pos0.data_ptr(), seg_slot, ns, max_q, a.heads, a.kv_heads, a.dim, a.vdim,
-                                            a.scale, R.o.data_ptr(), st))
-                _lib.check(lib.prl_gate_norm(R.o.data_ptr(), 1, ng, P + 4 * (nq + nk + nvk), ld, None, 1, ng, n, ng, 1, 0, 0,
+                if self.tc_attn[i] and not self.force_plain_attn:
+                    kv = self.k_pool[i].data_ptr()       # K pool, V pool right behind it (one "layer" of the Qwen2 pool layout)
+                    if decode:
+                        _lib.check(lib.prl_paged_attn_decode(R.q.data_ptr(), kv, self.n_pages, 1, 0, self.block_table.data_ptr(),
+                                                             self.max_blocks, self.seq_lens.data_ptr(), n, a.heads, a.kv_heads,
+                                                             a.dim, PAGE_SIZE, self.attn_splits[i], a.scale, R.ob.data_ptr(),
+                                                             self.attn_ws.data_ptr(), self.attn_ws.numel(), st))
+                    else:
+                        _lib.check(lib.prl_paged_attn_prefill_tc(R.q.data_ptr(), n, kv, self.n_pages, 1, 0,
+                                                                 self.block_table.data_ptr(), self.max_blocks, seg_start,
+                                                                 seg_len, seg_pos0.data_ptr(), seg_slot, ns, max_q, a.heads,
+                                                                 a.kv_heads, a.dim, PAGE_SIZE, a.scale, R.ob.data_ptr(), st))
+                    o_ptr, o_f32 = R.ob.data_ptr(), 0
+                else:
+                    _lib.check(lib.prl_attn_any(R.q.data_ptr(), self.k_pool[i].data_ptr(), self.v_pool[i].data_ptr(), f32,
+                                                self.block_table.data_ptr(), self.max_blocks, PAGE_SIZE, seg_start, seg_len,
+                                                seg_pos0.data_ptr(), seg_slot, ns, max_q, a.heads, a.kv_heads, a.dim, a.vdim,
+                                                a.scale, R.o.data_ptr(), st))
+                    o_ptr, o_f32 = R.o.data_ptr(), 1
+                _lib.check(lib.prl_gate_norm(o_ptr, o_f32, ng, P + 4 * (nq + nk + nvk), ld, None, 1, ng, n, ng, 1, 0, 0,
                                              eps, R.ya.data_ptr(), f32, st))
                 self._mm(R.ya, ng, w + "mix.left.o", W, R.y0, n)
                 # -- right: state-space mixer
@@ -439,7 +473,7 @@ class HybridEngine(EngineCore):
         _lib.check(lib.prl_decode_rows(self.active.data_ptr(), B, R.seg[1].data_ptr(), R.row_slot.data_ptr(), st))
         _lib.check(lib.prl_embed_scale(self.tokens.data_ptr(), self.arena.ptr("embed"), int(self.f32), cfg.embed_scale, B,
                                        cfg.width, cfg.vocab_size, R.x.data_ptr(), R.xa.data_ptr(), st))
-        self._layers(R, B, B, 1, self.positions, self.positions)
+        self._layers(R, B, B, 1, self.positions, self.positions, decode=True)
         _lib.check(lib.prl_rmsnorm_rows(R.x.data_ptr(), None, self.vec["final.norm"].data_ptr(), cfg.eps, B, cfg.width,
                                         R.xa.data_ptr(), int(self.f32), st))
         self._mm(R.xa, cfg.width, "head", cfg.vocab_size, self.logits, B)

@@ -251,3 +251,31 @@ def test_trace_runner_command_line(cuda_device, tmp_path):
         for i, ref in expect.items():
             got = torch.from_numpy(np.fromfile(out / f"{i}.f32", dtype="<f4")).view(-1, config["vocab"])
             assert got.shape == ref.shape and hc.rel_err(got, ref) < tol
+
+
+def test_head_size_128_runs_the_tcgen05_attention_kernels(cuda_device):
+    """bf16 with key = value size 128: the layer takes the chunked-prefill (tcgen05) and paged-decode kernels of the
+    Qwen2 engine, with its own score scale; against the oracle, against the any-geometry kernel, and through generation."""
+    from pipelinerl_b200.engine import SamplingParams
+    config = hc.model([hc.par_layer(heads=4, kv_heads=2, dim=128, vdim=128, rot=32, scale=0.11, mlp=hc.dense(ff=128)),
+                       hc.gla_layer(heads=2, dim=32, vdim=64, rank=8)], vocab=160, width=256)
+    wt = _weights(config, 21)
+    toks = hc.tokens_for(config, 300, seed=9)
+    ref = hc.oracle_logits(config, wt, toks)
+    eng = hc.build_engine(config, wt, torch.bfloat16, cuda_device, use_cuda_graph=True, max_seq_len=512)
+    assert eng.tc_attn[0]
+    fast = hc.stream_logits(eng, toks, [200, 2, 63, 1, 1])
+    assert hc.rel_err(fast, ref) < BF16_TOL
+    eng.force_plain_attn = True
+    plain = hc.stream_logits(eng, toks, [200, 2, 63, 1, 1])
+    eng.force_plain_attn = False
+    assert hc.rel_err(plain, ref) < BF16_TOL and hc.rel_err(fast, plain) < BF16_TOL
+    # decode steps through the CUDA graph: the paged-decode kernel reads what the prefill kernel's front end cached
+    prompts = [toks[:130], toks[:3]]
+    outs = eng.generate(prompts, SamplingParams(max_tokens=5, greedy=True, ignore_eos=True))
+    for p, r in zip(prompts, outs):
+        seq = list(p)
+        for tok, lp in zip(r.output_ids, r.output_logprobs):
+            lg = hc.oracle_logits(config, wt, seq)[-1]
+            assert abs(lp - torch.log_softmax(lg, -1)[tok].item()) < 0.15
+            seq.append(tok)
