@@ -587,10 +587,11 @@ int prl_gemm_any(const void* A, int32_t a_is_f32, int64_t lda, const void* W, in
 /* x = embed[token] * scale (fp32 residual) and xa = its copy in the operand type */
 int prl_embed_scale(const int32_t* tokens, const void* embed, int32_t f32, float scale, int32_t n, int32_t W,
                     int32_t vocab, float* x, void* xa, prl_stream_t stream);
-/* y = s0*y0 (+ s1*y1);  x += y / sqrt(mean(y^2) + eps) * gain;  xa = operand-type copy of x */
-int prl_postnorm_residual(const float* y0, int64_t ld0, float s0, const float* y1 /*or NULL*/, int64_t ld1, float s1,
-                          const float* gain, float eps, int32_t n, int32_t W, float* x, void* xa, int32_t f32,
-                          prl_stream_t stream);
+/* y = s0*y0 (+ s1*y1);  x += y / sqrt(mean(y^2) + eps) * gain;  xa = operand-type copy of x.  y0 / y1 may be split-K
+ * partials [n_split][n][ld] of prl_gemm_bf16_splitk: the slices are summed in order first */
+int prl_postnorm_residual(const float* y0, int64_t ld0, float s0, int32_t n_split0, const float* y1 /*or NULL*/, int64_t ld1,
+                          float s1, int32_t n_split1, const float* gain, float eps, int32_t n, int32_t W, float* x,
+                          void* xa, int32_t f32, prl_stream_t stream);
 /* out[i] = x[rows[i]] / rms * gain  (rows NULL = identity); the final norm in front of the head */
 int prl_rmsnorm_rows(const float* x, const int32_t* rows, const float* gain, float eps, int32_t n_out, int32_t W,
                      void* out, int32_t f32, prl_stream_t stream);

@@ -70,8 +70,16 @@ def _compile_one(src: Path, verbose: bool) -> tuple[Path, bool]:
     return obj, True
 
 
-def build(force: bool = False, verbose: bool = True) -> Path:
-    """Compile every csrc/*.cu for sm_100a and link pipelinerl_b200/_lib/libprl.so."""
+# what the sampler engines (engine.py, hybrid.py) call: enough for a command-line tool that only serves a model
+SAMPLER_SOURCES = ("prl_core.cu", "decode_ops.cu", "gemm_tc.cu", "gemm_tn.cu", "gemm_any.cu", "paged_attn.cu", "attn_tc.cu",
+                   "attn_any.cu", "hybrid_ops.cu", "lin_scan.cu")
+LINKED_LIST = LIB_DIR / "libprl.sources"
+
+
+def build(force: bool = False, verbose: bool = True, only=None) -> Path:
+    """Compile csrc/*.cu for sm_100a and link pipelinerl_b200/_lib/libprl.so.  `only` (file names) builds a library
+    with just those sources, e.g. SAMPLER_SOURCES for a tool that serves a model and never trains; a library that
+    already holds more is kept, and a later full build adds the rest."""
     OBJ_DIR.mkdir(parents=True, exist_ok=True)
     if force:
         for f in OBJ_DIR.glob("*.sha"):
@@ -79,10 +87,19 @@ def build(force: bool = False, verbose: bool = True) -> Path:
     srcs = _sources()
     if not srcs:
         raise RuntimeError("no CUDA sources found")
+    linked = set(LINKED_LIST.read_text().split()) if (LINKED_LIST.exists() and LIB_PATH.exists()) else set()
+    if only is not None:
+        need = set(only)
+        missing = need - {s.name for s in srcs}
+        if missing:
+            raise RuntimeError(f"unknown CUDA sources {sorted(missing)}")
+        names = linked if need <= linked else need | linked
+        srcs = [s for s in srcs if s.name in names]
     with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
         results = list(ex.map(lambda s: _compile_one(s, verbose), srcs))
     objs = [o for o, _ in results]
-    changed = any(c for _, c in results) or not LIB_PATH.exists()
+    names = {s.name for s in srcs}
+    changed = any(c for _, c in results) or not LIB_PATH.exists() or names != linked
     if changed:
         tmp = LIB_DIR / "libprl.so.tmp"
         cmd = [_nvcc(), "-shared", "-o", str(tmp), *map(str, objs),
@@ -92,8 +109,9 @@ def build(force: bool = False, verbose: bool = True) -> Path:
             sys.stderr.write(res.stdout + res.stderr)
             raise RuntimeError("link of libprl.so failed")
         os.replace(tmp, LIB_PATH)
+        LINKED_LIST.write_text("\n".join(sorted(names)) + "\n")
         if verbose:
-            print(f"[prl build] linked {LIB_PATH}")
+            print(f"[prl build] linked {LIB_PATH} ({len(names)} sources)")
     return LIB_PATH
 
 

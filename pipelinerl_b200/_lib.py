@@ -246,8 +246,9 @@ _SIGNATURES = {
                                C.c_int64, C.c_void_p, C.c_int64, C.c_void_p]),
     "prl_embed_scale": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_float, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
                                   C.c_void_p, C.c_void_p]),
-    "prl_postnorm_residual": (C.c_int, [C.c_void_p, C.c_int64, C.c_float, C.c_void_p, C.c_int64, C.c_float, C.c_void_p,
-                                        C.c_float, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
+    "prl_postnorm_residual": (C.c_int, [C.c_void_p, C.c_int64, C.c_float, C.c_int32, C.c_void_p, C.c_int64, C.c_float,
+                                        C.c_int32, C.c_void_p, C.c_float, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,
+                                        C.c_int32, C.c_void_p]),
     "prl_rmsnorm_rows": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int32, C.c_int32, C.c_void_p,
                                    C.c_int32, C.c_void_p]),
     "prl_gate_norm": (C.c_int, [C.c_void_p, C.c_int32, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int32, C.c_int32,
@@ -292,7 +293,11 @@ def load() -> C.CDLL:
                 "(the CUDA extension is the product; there is no CPU fallback)")
         lib = C.CDLL(str(_LIB_PATH))
         for name, (res, args) in _SIGNATURES.items():
-            fn = getattr(lib, name)  # AttributeError here = header / library mismatch
+            # a library built from a subset of the sources (_build.build(only=...)) lacks the other files' symbols:
+            # calling one of those raises AttributeError at the call site; tests/test_boundary.py checks the full build
+            fn = getattr(lib, name, None)
+            if fn is None:
+                continue
             fn.restype = res
             fn.argtypes = args
         _lib = lib

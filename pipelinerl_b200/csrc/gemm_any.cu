@@ -22,6 +22,8 @@ template <typename TA, typename TW>
 __global__ void __launch_bounds__(256) gemm_any_kernel(const TA* __restrict__ A, int64_t lda, const TW* __restrict__ W,
                                                        int64_t ldw, int M, int N, int K, float* __restrict__ C,
                                                        int64_t ldc) {
+  pdl_wait();   // launched with the programmatic-serialization attribute like the engine's other step kernels; no early
+                // trigger: letting the next grid become resident early measured +3 ms on a 4096-token prefill and +-0 on decode
   __shared__ float As[kStepK][kTile + 4];
   __shared__ float Ws[kStepK][kTile + 4];
   const int tid = threadIdx.x;
@@ -74,7 +76,7 @@ template <typename TA, typename TW>
 int launch_any(const void* A, int64_t lda, const void* W, int64_t ldw, int64_t M, int64_t N, int64_t K, float* C,
                int64_t ldc, cudaStream_t st) {
   dim3 grid((unsigned)((N + kTile - 1) / kTile), (unsigned)((M + kTile - 1) / kTile));
-  gemm_any_kernel<TA, TW><<<grid, 256, 0, st>>>((const TA*)A, lda, (const TW*)W, ldw, (int)M, (int)N, (int)K, C, ldc);
+  PRL_CUDA(launch_pdl((gemm_any_kernel<TA, TW>), dim3(grid), dim3(256), (size_t)(0), st, (const TA*)A, lda, (const TW*)W, ldw, (int)M, (int)N, (int)K, C, ldc));
   PRL_LAUNCH_CHECK();
   return PRL_OK;
 }

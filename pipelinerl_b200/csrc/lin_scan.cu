@@ -47,6 +47,7 @@ struct ScanArgs {
   // SSD scalars
   const float* dt_raw; int64_t ld_dt; int off_dt; int groups;
   const float* dt_bias; const float* a_log; const float* skip;
+  int vec4;   // every staged vector starts on a 16-byte boundary and dk, dv are multiples of 4: 16-byte cp.async
 };
 
 __device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
@@ -56,12 +57,18 @@ __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
   const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
 }
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 template <int R, int VC, bool SSD>
 __global__ void __launch_bounds__(kThreads) lin_scan_kernel(ScanArgs a) {
+  pdl_wait();   // launched with the programmatic-serialization attribute like the engine's other step kernels; no early
+                // trigger: letting the next grid become resident early measured +3 ms on a 4096-token prefill and +-0 on decode
   constexpr int kCols = kKeyLanes * VC;          // value columns per CTA
   constexpr int RS = R + 4;                      // padded stride of one thread's key-channel block (conflict-free LDS.128)
   constexpr int kVecTok = kKeyLanes * RS;        // floats per token and vector
@@ -111,18 +118,34 @@ __global__ void __launch_bounds__(kThreads) lin_scan_kernel(ScanArgs a) {
     float* ba = bq + kChunk * kVecTok;                       // GATED only
     float* bx = buf + kChunk * kNVec * kVecTok;
     float* bs = bx + kChunk * kCols;                         // SSD: raw dt per token
-    for (int t = 0; t < nt; ++t) {
-      const int64_t r = row0 + t0 + t;
-      for (int d = tid; d < dk; d += kThreads) {
-        const int o = t * kVecTok + (d / R) * RS + (d % R);
-        cp_async4(bk + o, kbase + r * a.ld_k + d);
-        cp_async4(bq + o, qbase + r * a.ld_q + d);
-        if (!SSD) cp_async4(ba + o, abase + r * a.ld_a + d);
+    if (R % 4 == 0 && a.vec4) {     // four key channels of one thread's block per copy
+      for (int t = 0; t < nt; ++t) {
+        const int64_t r = row0 + t0 + t;
+        for (int d = tid * 4; d < dk; d += kThreads * 4) {
+          const int o = t * kVecTok + (d / R) * RS + (d % R);
+          cp_async16(bk + o, kbase + r * a.ld_k + d);
+          cp_async16(bq + o, qbase + r * a.ld_q + d);
+          if (!SSD) cp_async16(ba + o, abase + r * a.ld_a + d);
+        }
       }
-    }
-    for (int i = tid; i < nt * kCols; i += kThreads) {
-      const int t = i / kCols, c = i % kCols;
-      if (c < cols_here) cp_async4(bx + t * kCols + c, xbase + (row0 + t0 + t) * a.ld_x + c);
+      for (int i = tid * 4; i < nt * kCols; i += kThreads * 4) {
+        const int t = i / kCols, c = i % kCols;
+        if (c < cols_here) cp_async16(bx + t * kCols + c, xbase + (row0 + t0 + t) * a.ld_x + c);
+      }
+    } else {
+      for (int t = 0; t < nt; ++t) {
+        const int64_t r = row0 + t0 + t;
+        for (int d = tid; d < dk; d += kThreads) {
+          const int o = t * kVecTok + (d / R) * RS + (d % R);
+          cp_async4(bk + o, kbase + r * a.ld_k + d);
+          cp_async4(bq + o, qbase + r * a.ld_q + d);
+          if (!SSD) cp_async4(ba + o, abase + r * a.ld_a + d);
+        }
+      }
+      for (int i = tid; i < nt * kCols; i += kThreads) {
+        const int t = i / kCols, c = i % kCols;
+        if (c < cols_here) cp_async4(bx + t * kCols + c, xbase + (row0 + t0 + t) * a.ld_x + c);
+      }
     }
     if (SSD && tid < nt) cp_async4(bs + tid, a.dt_raw + (row0 + t0 + tid) * a.ld_dt + a.off_dt + h);
     cp_async_commit();
@@ -245,7 +268,7 @@ int launch_one(const ScanArgs& a, int n_seg, cudaStream_t st) {
   static SmemAttr attr = {};
   if (smem > 48 * 1024) PRL_CUDA(ensure_smem(lin_scan_kernel<R, VC, SSD>, (int)smem, attr));
   dim3 grid((a.dv + kCols - 1) / kCols, a.heads, n_seg);
-  lin_scan_kernel<R, VC, SSD><<<grid, kThreads, smem, st>>>(a);
+  PRL_CUDA(launch_pdl((lin_scan_kernel<R, VC, SSD>), dim3(grid), dim3(kThreads), (size_t)(smem), st, a));
   PRL_LAUNCH_CHECK();
   return PRL_OK;
 }
@@ -260,8 +283,13 @@ int launch_r(const ScanArgs& a, int n_seg, cudaStream_t st) {
   return launch_one<R, 1, SSD>(a, n_seg, st);
 }
 
+inline bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
 template <bool SSD>
-int launch_scan(const ScanArgs& a, int n_seg, cudaStream_t st) {
+int launch_scan(ScanArgs a, int n_seg, cudaStream_t st) {
+  a.vec4 = (a.dk % 4 == 0 && a.dv % 4 == 0 && a.ld_k % 4 == 0 && a.ld_q % 4 == 0 && a.ld_x % 4 == 0 && a.off_k % 4 == 0 &&
+            a.off_q % 4 == 0 && a.off_x % 4 == 0 && aligned16(a.kvec) && aligned16(a.qvec) && aligned16(a.xval) &&
+            (SSD || (a.ld_a % 4 == 0 && aligned16(a.avec)))) ? 1 : 0;
   switch (plan_r(a.dk)) {
     case 1: return launch_r<1, SSD>(a, n_seg, st);
     case 2: return launch_r<2, SSD>(a, n_seg, st);
@@ -272,13 +300,11 @@ int launch_scan(const ScanArgs& a, int n_seg, cudaStream_t st) {
   }
 }
 
-__global__ void gla_decay_kernel(float* __restrict__ z, int64_t ldz, const float* __restrict__ bias, float inv_tau, int C,
-                                 int64_t total) {
-  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= total) return;
-  const int64_t r = i / C;
-  const int c = (int)(i - r * C);
-  float* p = z + r * ldz + c;
+__global__ void gla_decay_kernel(float* __restrict__ z, int64_t ldz, const float* __restrict__ bias, float inv_tau, int C) {
+  pdl_wait();
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float* p = z + (int64_t)blockIdx.x * ldz + c;
   *p = expf(logsigmoid_f(*p + bias[c]) * inv_tau);
 }
 
@@ -294,8 +320,7 @@ extern "C" int64_t prl_lin_scan_state_floats(int32_t heads, int32_t dk, int32_t 
 
 extern "C" int prl_gla_decay(float* z, int64_t ldz, const float* bias, float tau, int32_t n, int32_t C, prl_stream_t st) {
   PRL_CHECK_ARG(z && bias && n >= 1 && C >= 1 && ldz >= C && tau > 0.f, "prl_gla_decay: bad argument");
-  const int64_t total = (int64_t)n * C;
-  gla_decay_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)st>>>(z, ldz, bias, 1.f / tau, C, total);
+  PRL_CUDA(launch_pdl(gla_decay_kernel, dim3(n, (C + 255) / 256), dim3(256), (size_t)(0), (cudaStream_t)st, z, ldz, bias, 1.f / tau, C));
   PRL_LAUNCH_CHECK();
   return PRL_OK;
 }

@@ -284,8 +284,9 @@ class _Rows:
         self.ob = torch.zeros(n * wide_o if any(eng.tc_attn.values()) else 1, dtype=torch.bfloat16, device=d)  # tcgen05 attention out
         self.ya = torch.zeros(n * wide_o, dtype=T, device=d)    # gated / normed input of the output projection
         self.yb = torch.zeros(n * wide_o2, dtype=T, device=d)
-        self.y0 = torch.zeros(n * W, **f32)
-        self.y1 = torch.zeros(n * W, **f32)
+        ny = max(n, 16 * min(n, 128)) * W                       # up to 16 split-K slices of a <= 128-row projection
+        self.y0 = torch.zeros(ny, **f32)
+        self.y1 = torch.zeros(ny, **f32)
         self.q = torch.zeros(n * wide_q, dtype=T, device=d)
         self.act = torch.zeros(n * wide_f, dtype=T, device=d)
         self.tokens = torch.zeros(n, **i32)
@@ -365,17 +366,22 @@ class HybridEngine(EngineCore):
         return sum(L.attn.kv_heads * (L.attn.dim + L.attn.vdim) * e for L in self.cfg.layers if L.kind == "parallel")
 
     # ---- GEMM dispatch ------------------------------------------------------------------------------------------------
-    def _mm(self, src: torch.Tensor, K: int, w_name: str, N: int, out: torch.Tensor, n: int) -> None:
+    def _mm(self, src: torch.Tensor, K: int, w_name: str, N: int, out: torch.Tensor, n: int, split: bool = False) -> int:
         """out[n, N] (fp32) = src[n, K] @ W[N, K]^T.  bf16 with TMA-expressible sizes: the tcgen05 kernels (weight-
-        streaming swap-AB for n <= 128 rows, persistent CTA-pair kernel above); otherwise the CUDA-core kernel."""
+        streaming swap-AB for n <= 128 rows, persistent CTA-pair kernel above); otherwise the CUDA-core kernel.
+        `split`: the consumer sums split-K slices (prl_postnorm_residual), so a small-N projection of a decode step may
+        spread its K range over the SMs; returns the number of slices written ([slices][n][N])."""
         lib, st, wp = self.lib, self._st, self.arena.ptr(w_name)
         if self.f32 or self.force_plain_gemm or K % 8 or K < 64:
             _lib.check(lib.prl_gemm_any(src.data_ptr(), int(self.f32), K, wp, int(self.f32), K, n, N, K,
                                         out.data_ptr(), N, st))
         elif n <= 128:
-            _lib.check(lib.prl_gemm_bf16_splitk(wp, None, src.data_ptr(), n, N, K, 1, out.data_ptr(), st))
+            k = int(lib.prl_gemm_auto_split_k(n, N, K)) if split else 1
+            _lib.check(lib.prl_gemm_bf16_splitk(wp, None, src.data_ptr(), n, N, K, k, out.data_ptr(), st))
+            return k
         else:
             _lib.check(lib.prl_gemm_tn(src.data_ptr(), K, wp, K, n, N, K, out.data_ptr(), N, 1, 0, None, None, 0, 1.0, st))
+        return 1
 
     # ---- the layer program over n ragged rows -------------------------------------------------------------------------
     def _layers(self, R: _Rows, n: int, ns: int, max_q: int, row_pos: torch.Tensor, seg_pos0: torch.Tensor,
@@ -400,9 +406,9 @@ class HybridEngine(EngineCore):
                                             nv, st))
                 _lib.check(lib.prl_gate_norm(R.o.data_ptr(), 1, nv, P + 4 * (2 * nq + nv), ld, vec[w + "mix.norm"].data_ptr(),
                                              g.vdim, g.vdim, n, nv, 0, 0, 1, eps, R.ya.data_ptr(), f32, st))
-                self._mm(R.ya, nv, w + "mix.o", W, R.y0, n)
-                _lib.check(lib.prl_postnorm_residual(R.y0.data_ptr(), W, 1.0, None, 0, 0.0, vec[w + "norm1"].data_ptr(), eps,
-                                                     n, W, x, xa, f32, st))
+                k0 = self._mm(R.ya, nv, w + "mix.o", W, R.y0, n, split=True)
+                _lib.check(lib.prl_postnorm_residual(R.y0.data_ptr(), W, 1.0, k0, None, 0, 0.0, 1, vec[w + "norm1"].data_ptr(),
+                                                     eps, n, W, x, xa, f32, st))
             else:
                 a, s = L.attn, L.ssd
                 nq, nk, nvk, ng = a.heads * a.dim, a.kv_heads * a.dim, a.kv_heads * a.vdim, a.heads * a.vdim
@@ -438,7 +444,7 @@ class HybridEngine(EngineCore):
                     o_ptr, o_f32 = R.o.data_ptr(), 1
                 _lib.check(lib.prl_gate_norm(o_ptr, o_f32, ng, P + 4 * (nq + nk + nvk), ld, None, 1, ng, n, ng, 1, 0, 0,
                                              eps, R.ya.data_ptr(), f32, st))
-                self._mm(R.ya, ng, w + "mix.left.o", W, R.y0, n)
+                k0 = self._mm(R.ya, ng, w + "mix.left.o", W, R.y0, n, split=True)
                 # -- right: state-space mixer
                 inner, ch = s.inner, s.conv_channels
                 conv_w, conv_b = vec[w + "mix.right.conv"].data_ptr(), vec[w + "mix.right.conv.b"].data_ptr()
@@ -453,16 +459,16 @@ class HybridEngine(EngineCore):
                                             R.o2.data_ptr(), inner, st))
                 _lib.check(lib.prl_gate_norm(R.o2.data_ptr(), 1, inner, P + 4 * left, ld, vec[w + "mix.right.norm"].data_ptr(),
                                              inner, inner // s.norm_groups, n, inner, 0, 1, 1, eps, R.yb.data_ptr(), f32, st))
-                self._mm(R.yb, inner, w + "mix.right.o", W, R.y1, n)
-                _lib.check(lib.prl_postnorm_residual(R.y0.data_ptr(), W, L.left_scale, R.y1.data_ptr(), W, L.right_scale,
+                k1 = self._mm(R.yb, inner, w + "mix.right.o", W, R.y1, n, split=True)
+                _lib.check(lib.prl_postnorm_residual(R.y0.data_ptr(), W, L.left_scale, k0, R.y1.data_ptr(), W, L.right_scale, k1,
                                                      vec[w + "norm1"].data_ptr(), eps, n, W, x, xa, f32, st))
             if L.mlp is not None:
                 F = L.mlp.ff
                 self._mm(R.xa, W, w + "mlp.gate_up", 2 * F, R.P, n)
                 _lib.check(lib.prl_glu_clamped(P, 2 * F, n, F, L.mlp.limit, L.mlp.beta, R.act.data_ptr(), f32, st))
-                self._mm(R.act, F, w + "mlp.down", W, R.y0, n)
-                _lib.check(lib.prl_postnorm_residual(R.y0.data_ptr(), W, 1.0, None, 0, 0.0, vec[w + "norm2"].data_ptr(), eps,
-                                                     n, W, x, xa, f32, st))
+                k0 = self._mm(R.act, F, w + "mlp.down", W, R.y0, n, split=True)
+                _lib.check(lib.prl_postnorm_residual(R.y0.data_ptr(), W, 1.0, k0, None, 0, 0.0, 1, vec[w + "norm2"].data_ptr(),
+                                                     eps, n, W, x, xa, f32, st))
             if trace is not None:
                 trace.append(R.x[:n * W].view(n, W).clone())
 

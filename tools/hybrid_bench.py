@@ -183,7 +183,7 @@ def kernel_table(eng, s, batch, chunk, timer):
         out[f"conv_silu/{shape}"] = dict(ms=round(ms, 4), hbm_frac=round(n * ch * 8 / ms / 1e6 / hbm, 3))
 
         def post():
-            _lib.check(lib.prl_postnorm_residual(R.y0.data_ptr(), W, 1.0, R.y1.data_ptr(), W, 1.0, vec[wp + "norm1"].data_ptr(),
+            _lib.check(lib.prl_postnorm_residual(R.y0.data_ptr(), W, 1.0, 1, R.y1.data_ptr(), W, 1.0, 1, vec[wp + "norm1"].data_ptr(),
                                                  cfg.eps, n, W, R.x.data_ptr(), R.xa.data_ptr(), 0, st))
         ms = timer.events(post)
         out[f"postnorm_residual/{shape}"] = dict(ms=round(ms, 4), hbm_frac=round(n * W * (4 * 4 + 2) / ms / 1e6 / hbm, 3))
@@ -221,7 +221,7 @@ def kernel_table(eng, s, batch, chunk, timer):
     return out
 
 
-def run(sizes, prompt, context, batch, steps, warm, kernels=True):
+def run(sizes, prompt, context, batch, steps, warm, kernels=True, e2e=True):
     from pipelinerl_b200.engine import DecodeEngine
     from pipelinerl_b200.hybrid import HybridConfig, HybridEngine
     from pipelinerl_b200.model import ModelConfig, ParamArena
@@ -234,18 +234,21 @@ def run(sizes, prompt, context, batch, steps, warm, kernels=True):
                   prefill_chunk=1024)
         qcfg = ModelConfig(vocab_size=s["vocab"], hidden_size=s["width"], intermediate_size=s["ff"], num_layers=s["layers"],
                            num_q_heads=s["heads"], num_kv_heads=s["kv"])
-        eng = DecodeEngine(qcfg, ParamArena(qcfg, dev).init_random(seed=1), **kw)
-        q = end_to_end(eng, s["vocab"], prompt, context, batch, steps, warm)
-        q["params_M"] = round(qcfg.num_params() / 1e6)
-        del eng
-        torch.cuda.empty_cache()
         hcfg = HybridConfig.from_povurax(hybrid_config(s))
+        entry = {}
+        if e2e:
+            eng = DecodeEngine(qcfg, ParamArena(qcfg, dev).init_random(seed=1), **kw)
+            q = end_to_end(eng, s["vocab"], prompt, context, batch, steps, warm)
+            q["params_M"] = round(qcfg.num_params() / 1e6)
+            del eng
+            torch.cuda.empty_cache()
         eng = HybridEngine(hcfg, ParamArena(hcfg, dev).init_random(seed=1), **kw)
-        h = end_to_end(eng, s["vocab"], prompt, context, batch, steps, warm)
-        h["params_M"] = round(hcfg.num_params() / 1e6)
-        entry = {"qwen2": q, "hybrid": h,
-                 "hybrid_over_qwen2": {"prefill": round(h["prefill_tokens_per_s"] / q["prefill_tokens_per_s"], 3),
-                                       "decode": round(h["decode_tokens_per_s"] / q["decode_tokens_per_s"], 3)}}
+        if e2e:
+            h = end_to_end(eng, s["vocab"], prompt, context, batch, steps, warm)
+            h["params_M"] = round(hcfg.num_params() / 1e6)
+            entry = {"qwen2": q, "hybrid": h,
+                     "hybrid_over_qwen2": {"prefill": round(h["prefill_tokens_per_s"] / q["prefill_tokens_per_s"], 3),
+                                           "decode": round(h["decode_tokens_per_s"] / q["decode_tokens_per_s"], 3)}}
         if kernels:
             entry["kernels"] = kernel_table(eng, s, batch, 1024, timer)
         res[name] = entry
@@ -263,10 +266,11 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-kernels", action="store_true")
+    ap.add_argument("--only-kernels", action="store_true", help="skip the end-to-end runs (a small case for a profiler)")
     a = ap.parse_args()
     from pipelinerl_b200 import _lib
     before = _lib.launch_count()
-    res = run(a.sizes.split(","), a.prompt, a.context, a.batch, a.steps, a.warmup, kernels=not a.no_kernels)
+    res = run(a.sizes.split(","), a.prompt, a.context, a.batch, a.steps, a.warmup, kernels=not a.no_kernels, e2e=not a.only_kernels)
     print(json.dumps({"bench": "hybrid_vs_qwen2", "dtype": "bf16", "data": "synthetic", "prompt": a.prompt,
                       "context": a.context, "batch": a.batch, "steps": a.steps, "warmup": a.warmup,
                       "gpu_launches": _lib.launch_count() - before, "sizes": res}), flush=True)
