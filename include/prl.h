@@ -636,6 +636,14 @@ int prl_ssd_scan(const float* P, int64_t ldp, int32_t off_dt, const float* xbc, 
                  int32_t n_state, int32_t dv, const int32_t* seg_start, const int32_t* seg_len,
                  const int32_t* seg_slot, int32_t n_seg, float* state, float* out, int64_t ld_out,
                  prl_stream_t stream);
+/* gate_up GEMM with the clamped gate in its epilogue (the SwiGLU-epilogue kernels of the Qwen2 engine with another
+ * activation): act[M, I] bf16 = g * sigmoid(beta * g) * (u + 1), g = min(gate, limit), u = clamp(up, +-limit), of the
+ * fp32 accumulators; W = [gate rows; up rows].  _decode: 1 <= M <= 128, I % 64 == 0 (weight-streaming kernel);
+ * _f32: any M, I % 128 == 0 (persistent CTA-pair kernel). */
+int prl_gemm_glu_clamped_decode(const void* W, const void* X, int64_t M, int64_t I, int64_t K, float limit, float beta,
+                                void* act_bf16, prl_stream_t stream);
+int prl_gemm_glu_clamped_f32(const void* X_bf16, int64_t ldx, const void* W_gate_up_bf16, int64_t ldw, int64_t M, int64_t I,
+                             int64_t K, float limit, float beta, void* act_bf16, int64_t ld_act, prl_stream_t stream);
 /* decode step: per-slot engine state -> ragged-row metadata (seg_len = active, row_slot = slot or -1) */
 int prl_decode_rows(const uint8_t* active, int32_t B, int32_t* seg_len, int32_t* row_slot, prl_stream_t stream);
 

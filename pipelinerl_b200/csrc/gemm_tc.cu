@@ -134,6 +134,9 @@ struct GemmParams {
   // act[token, feature] = bf16(SiLU(gate) * up) -- the bits of the partial tile + silu_mul_kernel pair, without the pair
   int64_t swiglu_I;         // 0 = off
   __nv_bfloat16* act;       // [M, swiglu_I]
+  // gated activation of the epilogue: glu_limit == 0: SiLU(gate) * up; glu_limit > 0: the clamped form of the hybrid decoders,
+  // g = min(gate, limit), u = clamp(up, +-limit), act = g * sigmoid(glu_beta * g) * (u + 1)
+  float glu_limit, glu_beta;
 };
 
 template <int kNTile>
@@ -311,7 +314,14 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             for (int j = 0; j < kChunk; ++j) {
               if (c0 + j < m_valid) {
                 const float gg = __uint_as_float(v[j]), uu = xch[(c0 + j) * 64 + r];
-                p.act[(int64_t)(m0 + c0 + j) * p.swiglu_I + f] = __float2bfloat16_rn((gg / (1.f + __expf(-gg))) * uu);
+                float av;
+                if (p.glu_limit > 0.f) {
+                  const float gc = fminf(gg, p.glu_limit), uc = fminf(fmaxf(uu, -p.glu_limit), p.glu_limit);
+                  av = gc / (1.f + __expf(-p.glu_beta * gc)) * (uc + 1.f);
+                } else {
+                  av = (gg / (1.f + __expf(-gg))) * uu;
+                }
+                p.act[(int64_t)(m0 + c0 + j) * p.swiglu_I + f] = __float2bfloat16_rn(av);
               }
             }
           }
@@ -672,8 +682,8 @@ static int gemm_splitk_impl(const void* W, const void* W_lo, const void* X, int6
 // Token-step gate_up GEMM with SiLU(gate) * up in its epilogue (sampler side, M <= 128 tokens, no split-K: 2 I / 128 tiles
 // already fill the SMs): act[M, I] bf16 = the bits prl_gemm_bf16_splitk(split_k = 1) + prl_silu_mul produce, one launch and
 // no [M, 2 I] fp32 tile in between.  W = gate_up_proj [2 I, K] as stored (gate rows first).
-extern "C" int prl_gemm_swiglu_decode(const void* W, const void* X, int64_t M, int64_t I, int64_t K, void* act_bf16,
-                                      prl_stream_t stream_) {
+static int gemm_glu_decode_impl(const void* W, const void* X, int64_t M, int64_t I, int64_t K, float glu_limit, float glu_beta,
+                                void* act_bf16, prl_stream_t stream_) {
   PRL_CHECK_ARG(W && X && act_bf16, "prl_gemm_swiglu_decode: NULL argument");
   PRL_CHECK_ARG(M >= 1 && M <= 128 && I >= 64 && I % 64 == 0 && K >= 8 && K % 8 == 0,
                 "prl_gemm_swiglu_decode: need 1 <= M <= 128, I %% 64 == 0, K %% 8 == 0 (M=%lld I=%lld K=%lld)", (long long)M,
@@ -682,7 +692,7 @@ extern "C" int prl_gemm_swiglu_decode(const void* W, const void* X, int64_t M, i
   const int nt = pick_ntile(M);
   GemmParams p = {};
   p.M = M; p.N = 2 * I; p.K = K; p.kblocks = (int)((K + kBlockK - 1) / kBlockK); p.split_k = 1;
-  p.swiglu_I = I; p.act = (__nv_bfloat16*)act_bf16;
+  p.swiglu_I = I; p.act = (__nv_bfloat16*)act_bf16; p.glu_limit = glu_limit; p.glu_beta = glu_beta;
   CUtensorMap tw, tx;
   int rc = make_tmap_2d_bf16(&tw, W, (uint64_t)K, (uint64_t)(2 * I), (uint64_t)K * 2, kBlockK, 64);   // 64-row boxes
   if (rc) return rc;
@@ -695,6 +705,19 @@ extern "C" int prl_gemm_swiglu_decode(const void* W, const void* X, int64_t M, i
     case 64: return launch_gemm<64>(tw, tw, tx, p, stream);
     default: return launch_gemm<128>(tw, tw, tx, p, stream);
   }
+}
+
+extern "C" int prl_gemm_swiglu_decode(const void* W, const void* X, int64_t M, int64_t I, int64_t K, void* act_bf16,
+                                      prl_stream_t stream_) {
+  return gemm_glu_decode_impl(W, X, M, I, K, 0.f, 0.f, act_bf16, stream_);
+}
+
+// the same kernel with the clamped gate of the hybrid decoders in its epilogue (csrc/hybrid_ops.cu glu_clamped_kernel's formula
+// on the fp32 accumulators): act = g * sigmoid(beta * g) * (u + 1), g = min(gate, limit), u = clamp(up, +-limit)
+extern "C" int prl_gemm_glu_clamped_decode(const void* W, const void* X, int64_t M, int64_t I, int64_t K, float limit, float beta,
+                                           void* act_bf16, prl_stream_t stream_) {
+  PRL_CHECK_ARG(limit > 0.f, "prl_gemm_glu_clamped_decode: limit must be positive");
+  return gemm_glu_decode_impl(W, X, M, I, K, limit, beta, act_bf16, stream_);
 }
 
 extern "C" int prl_gemm_bf16_splitk(const void* W, const void* W_lo, const void* X, int64_t M, int64_t N, int64_t K,

@@ -55,6 +55,9 @@ struct TnParams {
   int swiglu_fp32;      // 1: SiLU(gate) * up of the fp32 ACCUMULATORS (the sampler's rounding points, decode_ops.cu silu_mul_kernel)
   __nv_bfloat16* act;      // [M, ld_act]
   int64_t ld_act;
+  // glu_limit > 0 (with swiglu_fp32): the clamped gate of the hybrid decoders instead of SiLU(gate) * up:
+  // g = min(gate, limit), u = clamp(up, +-limit), act = g * sigmoid(glu_beta * g) * (u + 1)
+  float glu_limit, glu_beta;
   // head epilogue (kHead): logits never leave TMEM/registers
   const int64_t* targets;  // [M] or NULL
   float4* head_part;       // [n_tiles, M]: (max, sum exp, sum exp*z, target logit or -inf) of one 256-column vocabulary tile
@@ -315,6 +318,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
               if (p.swiglu_fp32) {   // sampler prefill: identical bits to the fp32 GEMM output + silu_mul_kernel pair
                 const float g0 = __uint_as_float(rg[j + 2 * e]), g1 = __uint_as_float(rg[j + 2 * e + 1]);
                 const float u0 = __uint_as_float(ru[j + 2 * e]), u1 = __uint_as_float(ru[j + 2 * e + 1]);
+                if (p.glu_limit > 0.f) {
+                  const float l = p.glu_limit, b = p.glu_beta;
+                  const float c0g = fminf(g0, l), c1g = fminf(g1, l);
+                  const float c0u = fminf(fmaxf(u0, -l), l), c1u = fminf(fmaxf(u1, -l), l);
+                  ha[e] = __floats2bfloat162_rn(c0g / (1.f + __expf(-b * c0g)) * (c0u + 1.f),
+                                                c1g / (1.f + __expf(-b * c1g)) * (c1u + 1.f));
+                  continue;
+                }
                 ha[e] = __floats2bfloat162_rn((g0 / (1.f + __expf(-g0))) * u0, (g1 / (1.f + __expf(-g1))) * u1);
                 continue;
               }
@@ -619,7 +630,8 @@ extern "C" int prl_gemm_dgrad_swiglu(const void* dY, int64_t ldy, const void* W_
 // gate_up GEMM with the SwiGLU activation in its epilogue: act[M, I] = silu(X Wg^T) * (X Wu^T), W = [Wg; Wu] ([2 I, K]).
 // gate_up (bf16 [M, 2 I], may be NULL) is written as well when the backward will need it.
 static int gemm_swiglu_impl(const void* X, int64_t ldx, const void* W, int64_t ldw, int64_t M, int64_t I, int64_t K,
-                            void* act, int64_t ld_act, void* gate_up, int64_t ld_gu, int fp32_act, prl_stream_t stream_);
+                            void* act, int64_t ld_act, void* gate_up, int64_t ld_gu, int fp32_act, prl_stream_t stream_,
+                            float glu_limit = 0.f, float glu_beta = 0.f);
 
 extern "C" int prl_gemm_swiglu(const void* X, int64_t ldx, const void* W, int64_t ldw, int64_t M, int64_t I, int64_t K,
                                void* act, int64_t ld_act, void* gate_up, int64_t ld_gu, prl_stream_t stream_) {
@@ -634,8 +646,17 @@ extern "C" int prl_gemm_swiglu_f32(const void* X, int64_t ldx, const void* W, in
   return gemm_swiglu_impl(X, ldx, W, ldw, M, I, K, act, ld_act, nullptr, 0, 1, stream_);
 }
 
+// the sampler form with the clamped gate of the hybrid decoders: act = g * sigmoid(beta * g) * (u + 1) of the fp32 accumulators,
+// g = min(gate, limit), u = clamp(up, +-limit)
+extern "C" int prl_gemm_glu_clamped_f32(const void* X, int64_t ldx, const void* W, int64_t ldw, int64_t M, int64_t I, int64_t K,
+                                        float limit, float beta, void* act, int64_t ld_act, prl_stream_t stream_) {
+  PRL_CHECK_ARG(limit > 0.f, "prl_gemm_glu_clamped_f32: limit must be positive");
+  return gemm_swiglu_impl(X, ldx, W, ldw, M, I, K, act, ld_act, nullptr, 0, 1, stream_, limit, beta);
+}
+
 static int gemm_swiglu_impl(const void* X, int64_t ldx, const void* W, int64_t ldw, int64_t M, int64_t I, int64_t K,
-                            void* act, int64_t ld_act, void* gate_up, int64_t ld_gu, int fp32_act, prl_stream_t stream_) {
+                            void* act, int64_t ld_act, void* gate_up, int64_t ld_gu, int fp32_act, prl_stream_t stream_,
+                            float glu_limit, float glu_beta) {
   PRL_CHECK_ARG(X && W && act, "prl_gemm_swiglu: NULL argument");
   PRL_CHECK_ARG(M >= 1 && I >= kHalf && I % kHalf == 0 && K >= 8, "prl_gemm_swiglu: need I %% 128 == 0 (M=%lld I=%lld K=%lld)",
                 (long long)M, (long long)I, (long long)K);
@@ -650,6 +671,7 @@ static int gemm_swiglu_impl(const void* X, int64_t ldx, const void* W, int64_t l
   p.n_tiles = (int)(I / kHalf);
   p.C = gate_up; p.ldc = ld_gu; p.alpha = 1.f;
   p.swiglu_I = I; p.swiglu_fp32 = fp32_act; p.act = (__nv_bfloat16*)act; p.ld_act = ld_act;
+  p.glu_limit = glu_limit; p.glu_beta = glu_beta;
   CUtensorMap ta, tb;
   int rc = make_tmap_2d_bf16(&ta, X, (uint64_t)K, (uint64_t)M, (uint64_t)ldx * 2, kBK, kHalf);
   if (rc) return rc;

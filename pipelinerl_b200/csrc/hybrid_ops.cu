@@ -314,7 +314,8 @@ extern "C" int prl_postnorm_residual(const float* y0, int64_t ld0, float s0, int
                 (!y1 || n_split1 >= 1), "prl_postnorm_residual: bad argument");
   const int64_t st0 = (int64_t)n * ld0, st1 = (int64_t)n * ld1;
   int th = ((W + 31) / 32) * 32;
-  th = th > 1024 ? 1024 : th;
+  const int cap = n <= 256 ? 1024 : 256;     // few rows: more threads per row; many rows: more rows per SM
+  th = th > cap ? cap : th;
   const int keep = (size_t)W * sizeof(float) <= 40 * 1024 ? 1 : 0;
   const size_t smem = keep ? (size_t)W * sizeof(float) : 0;
   if (f32) PRL_CUDA(launch_pdl(postnorm_residual_kernel<float>, dim3(n), dim3(th), smem, (cudaStream_t)st, y0, ld0, s0, n_split0, st0, y1, ld1, s1, n_split1, st1, gain, eps, W, keep, x, (float*)xa));

@@ -306,6 +306,7 @@ class HybridEngine(EngineCore):
         if self.op_dtype not in (torch.float32, torch.bfloat16):
             raise ValueError("the hybrid engine runs bf16 or fp32 weights")
         self.force_plain_gemm = False      # tests: route every GEMM through the CUDA-core kernel
+        self.unfused_glu = False           # tests: gate_up GEMM + activation kernel instead of the GEMM's gated epilogue
         self.force_plain_attn = False      # tests: the any-geometry attention kernel also where the tcgen05 ones fit
         self._rows: _Rows | None = None
         super().__init__(cfg, arena, **kw)
@@ -464,8 +465,17 @@ class HybridEngine(EngineCore):
                                                      vec[w + "norm1"].data_ptr(), eps, n, W, x, xa, f32, st))
             if L.mlp is not None:
                 F = L.mlp.ff
-                self._mm(R.xa, W, w + "mlp.gate_up", 2 * F, R.P, n)
-                _lib.check(lib.prl_glu_clamped(P, 2 * F, n, F, L.mlp.limit, L.mlp.beta, R.act.data_ptr(), f32, st))
+                tc = not (self.f32 or self.force_plain_gemm or W % 8 or W < 64 or self.unfused_glu)
+                if tc and n <= 128 and F % 64 == 0:
+                    # the clamped gate in the gate_up GEMM's epilogue (the Qwen2 step's SwiGLU-epilogue kernel): no [n, 2F] tile
+                    _lib.check(lib.prl_gemm_glu_clamped_decode(self.arena.ptr(w + "mlp.gate_up"), xa, n, F, W, L.mlp.limit,
+                                                               L.mlp.beta, R.act.data_ptr(), st))
+                elif tc and n > 128 and F % 128 == 0:
+                    _lib.check(lib.prl_gemm_glu_clamped_f32(xa, W, self.arena.ptr(w + "mlp.gate_up"), W, n, F, W, L.mlp.limit,
+                                                            L.mlp.beta, R.act.data_ptr(), F, st))
+                else:
+                    self._mm(R.xa, W, w + "mlp.gate_up", 2 * F, R.P, n)
+                    _lib.check(lib.prl_glu_clamped(P, 2 * F, n, F, L.mlp.limit, L.mlp.beta, R.act.data_ptr(), f32, st))
                 k0 = self._mm(R.act, F, w + "mlp.down", W, R.y0, n, split=True)
                 _lib.check(lib.prl_postnorm_residual(R.y0.data_ptr(), W, 1.0, k0, None, 0, 0.0, 1, vec[w + "norm2"].data_ptr(),
                                                      eps, n, W, x, xa, f32, st))

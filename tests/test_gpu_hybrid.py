@@ -270,6 +270,12 @@ def test_head_size_128_runs_the_tcgen05_attention_kernels(cuda_device):
     plain = hc.stream_logits(eng, toks, [200, 2, 63, 1, 1])
     eng.force_plain_attn = False
     assert hc.rel_err(plain, ref) < BF16_TOL and hc.rel_err(fast, plain) < BF16_TOL
+    # ff = 128: the clamped gate runs in the gate_up GEMM's epilogue (both the 200-row and the few-row kernel); against
+    # the separate activation kernel on the fp32 GEMM output
+    eng.unfused_glu = True
+    unfused = hc.stream_logits(eng, toks, [200, 2, 63, 1, 1])
+    eng.unfused_glu = False
+    assert hc.rel_err(unfused, ref) < BF16_TOL and hc.rel_err(fast, unfused) < 0.25 * BF16_TOL
     # decode steps through the CUDA graph: the paged-decode kernel reads what the prefill kernel's front end cached
     prompts = [toks[:130], toks[:3]]
     outs = eng.generate(prompts, SamplingParams(max_tokens=5, greedy=True, ignore_eos=True))
