@@ -108,10 +108,23 @@ class HybridConfig:
         """config.json of a Povurax checkpoint.  The rank of a GLA layer's decay bottleneck is not a config key: it is
         the row count of the layer's `mix.a1` tensor (tensor_shapes), or `mixer.rank` when building without a file."""
         layers = []
+        n_layers = len(d["layers"])
+
+        def owner(i: int) -> int:
+            """The layer whose tensors layer i runs with: follow `weights_of` to a layer that has its own."""
+            seen = set()
+            while "weights_of" in d["layers"][i] and int(d["layers"][i]["weights_of"]) != i:
+                if i in seen:
+                    raise ValueError(f"layer {i}: weights_of runs in a circle")
+                seen.add(i)
+                i = int(d["layers"][i]["weights_of"])
+                if not 0 <= i < n_layers:
+                    raise ValueError(f"weights_of names layer {i}, which does not exist")
+            return i
         for i, L in enumerate(d["layers"]):
-            j = int(L.get("weights_of", i))
-            if j != i and not (0 <= j < i and "weights_of" not in d["layers"][j]):
-                raise ValueError(f"layer {i}: weights_of must name an earlier layer that has its own tensors")
+            j = owner(i)
+            if L["type"] != d["layers"][j]["type"]:
+                raise ValueError(f"layer {i} ({L['type']}) cannot run with the tensors of layer {j} ({d['layers'][j]['type']})")
             m = L["mixer"]
             mlp = None
             if L.get("mlp") is not None:

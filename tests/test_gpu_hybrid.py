@@ -276,6 +276,15 @@ def test_head_size_128_runs_the_tcgen05_attention_kernels(cuda_device):
     unfused = hc.stream_logits(eng, toks, [200, 2, 63, 1, 1])
     eng.unfused_glu = False
     assert hc.rel_err(unfused, ref) < BF16_TOL and hc.rel_err(fast, unfused) < 0.25 * BF16_TOL
+    # two requests in one batch (a portion beside a single token, then the reverse) against each alone
+    a, b = toks[:150], toks[150:260]
+    alone_a, alone_b = hc.stream_logits(eng, a, [len(a)]), hc.stream_logits(eng, b, [len(b)])
+    sa, sb = eng.open_stream(), eng.open_stream()
+    l1 = eng.feed([(sa, a[:149], list(range(149))), (sb, b[:1], [0])]).double().cpu()
+    l2 = eng.feed([(sb, b[1:], list(range(109))), (sa, a[149:], [0])]).double().cpu()
+    eng.close_stream(sa), eng.close_stream(sb)
+    assert hc.rel_err(torch.cat([l1[:149], l2[109:]]), alone_a) < 0.25 * BF16_TOL
+    assert hc.rel_err(torch.cat([l1[149:], l2[:109]]), alone_b) < 0.25 * BF16_TOL
     # decode steps through the CUDA graph: the paged-decode kernel reads what the prefill kernel's front end cached
     prompts = [toks[:130], toks[:3]]
     outs = eng.generate(prompts, SamplingParams(max_tokens=5, greedy=True, ignore_eos=True))
@@ -285,3 +294,42 @@ def test_head_size_128_runs_the_tcgen05_attention_kernels(cuda_device):
             lg = hc.oracle_logits(config, wt, seq)[-1]
             assert abs(lp - torch.log_softmax(lg, -1)[tok].item()) < 0.15
             seq.append(tok)
+
+
+def test_rollouts_through_the_plugin_interface(cuda_device):
+    """The family behind the framework's serving thread and LLM handle (serving.EngineServer, llm.TrainableLLM,
+    actor.schedule_rollouts with the synthetic rollout plugin): temperature-1 sampling by the engine's own sampler, more
+    rollouts than slots, and every returned logprob equal to the oracle's log-softmax at the sampled token."""
+    import asyncio
+    from pipelinerl_b200.actor import schedule_rollouts
+    from pipelinerl_b200.domains.synthetic import load_problems
+    from pipelinerl_b200.llm import SyntheticTokenizer, TrainableLLM
+    from pipelinerl_b200.serving import EngineServer
+    config = hc.model([hc.gla_layer(mlp=hc.dense()), hc.par_layer(mlp=hc.dense(ff=48))], vocab=96, width=64)
+    wt = _weights(config, 31)
+    eng = hc.build_engine(config, wt, torch.float32, cuda_device, max_batch=3, max_seq_len=128, max_new_tokens=16,
+                          use_cuda_graph=True, eos_id=2)
+    server = EngineServer("hybrid-sampler", eng).start()
+    try:
+        llm = TrainableLLM(server.base_url, "tiny-hybrid", parameters={"max_tokens": 7, "temperature": 1.0},
+                           tokenizer=SyntheticTokenizer(vocab_size=config["vocab"]))
+        problems = load_problems(["train"], n_problems=3, prompt_tokens=21, vocab_limit=config["vocab"])
+        groups = []
+        stats = asyncio.run(schedule_rollouts(None, 3, problems, [llm],
+                                              "pipelinerl_b200.domains.synthetic.generate_synthetic_rollout", groups.append,
+                                              get_model_version=lambda: 0))
+        assert stats["groups"] == 3 and stats["finished"] == 9
+    finally:
+        server.stop()
+    checked = 0
+    for group in groups:
+        for result in group:
+            text = result.training_texts[0]
+            ids, lps = list(text.input_ids), list(text.logprobs)
+            n_prompt = len(ids) - len(lps)
+            assert n_prompt == 21 and 1 <= len(lps) <= 7
+            ref = torch.log_softmax(hc.oracle_logits(config, wt, ids[:-1]), -1)
+            for k, lp in enumerate(lps):
+                assert abs(lp - ref[n_prompt - 1 + k, ids[n_prompt + k]].item()) < 2e-3
+                checked += 1
+    assert checked >= 9

@@ -37,12 +37,18 @@ def test_config_rejects_what_the_design_does_not_have():
     bad = hc.model([hc.gla_layer(mlp=dict(kind="experts", ff=8, limit=1.0))])
     with pytest.raises(ValueError):
         HybridConfig.from_povurax(bad)
-    bad = hc.model([hc.gla_layer(), hc.shared(hc.gla_layer(), 2), hc.gla_layer()])      # weights_of points forward
+    bad = hc.model([hc.gla_layer(), hc.shared(hc.gla_layer(), 2), hc.shared(hc.gla_layer(), 1)])    # a circle
     with pytest.raises(ValueError):
         HybridConfig.from_povurax(bad)
-    bad = hc.model([hc.gla_layer(), hc.shared(hc.gla_layer(), 0), hc.shared(hc.gla_layer(), 1)])   # ... at a layer without tensors
+    bad = hc.model([hc.gla_layer(), hc.shared(hc.par_layer(), 0)])                                 # another kind of mixer
     with pytest.raises(ValueError):
         HybridConfig.from_povurax(bad)
+    bad = hc.model([hc.gla_layer(), hc.shared(hc.gla_layer(), 7)])
+    with pytest.raises(ValueError):
+        HybridConfig.from_povurax(bad)
+    chain = HybridConfig.from_povurax(hc.model([hc.gla_layer(), hc.shared(hc.gla_layer(), 0), hc.shared(hc.gla_layer(), 1),
+                                                hc.shared(hc.gla_layer(), 4), hc.gla_layer()]))
+    assert [L.weights_of for L in chain.layers] == [0, 0, 0, 4, 4]       # chains and forward references resolve to the owner
     bad = hc.model([hc.par_layer(heads=3, kv_heads=2)])
     with pytest.raises(ValueError):
         HybridConfig.from_povurax(bad)
