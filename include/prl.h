@@ -636,6 +636,25 @@ int prl_ssd_scan(const float* P, int64_t ldp, int32_t off_dt, const float* xbc, 
                  int32_t n_state, int32_t dv, const int32_t* seg_start, const int32_t* seg_len,
                  const int32_t* seg_slot, int32_t n_seg, float* state, float* out, int64_t ld_out,
                  prl_stream_t stream);
+/* The same recurrences with every segment cut into pieces that run side by side (a long prompt portion of one
+ * sequence otherwise is a dependent chain on a handful of CTAs): each piece is scanned from a zero state, the pieces'
+ * states are chained per segment, and the incoming state's share of every output is added as a small matrix product.
+ * Same result up to fp32 rounding.  Pieces are rows sub_start[i] .. + sub_len[i] of the batch, in order, at most
+ * prl_lin_scan_piece_tokens() each; segment s owns pieces seg_sub0[s] .. + seg_nsub[s].  scratch (16-byte aligned):
+ * n_sub * prl_lin_scan_state_floats() floats; piece_decay: n_sub * prl_lin_scan_piece_decay_floats() floats. */
+int32_t prl_lin_scan_piece_tokens(void);
+int64_t prl_lin_scan_piece_decay_floats(int32_t heads, int32_t dk);
+int prl_gla_scan_split(const float* P, int64_t ldp, int32_t off_q, int32_t off_k, int32_t off_v, float q_scale,
+                       const float* decay, int64_t ld_decay, int32_t heads, int32_t dk, int32_t dv,
+                       const int32_t* seg_slot, int32_t n_seg, const int32_t* seg_sub0, const int32_t* seg_nsub,
+                       const int32_t* sub_start, const int32_t* sub_len, int32_t n_sub, float* scratch,
+                       float* piece_decay, float* state, float* out, int64_t ld_out, prl_stream_t stream);
+int prl_ssd_scan_split(const float* P, int64_t ldp, int32_t off_dt, const float* xbc, int64_t ld_xbc,
+                       const float* dt_bias, const float* a_log, const float* skip, int32_t heads, int32_t groups,
+                       int32_t n_state, int32_t dv, const int32_t* seg_slot, int32_t n_seg,
+                       const int32_t* seg_sub0, const int32_t* seg_nsub, const int32_t* sub_start,
+                       const int32_t* sub_len, int32_t n_sub, float* scratch, float* piece_decay, float* state,
+                       float* out, int64_t ld_out, prl_stream_t stream);
 /* gate_up GEMM with the clamped gate in its epilogue (the SwiGLU-epilogue kernels of the Qwen2 engine with another
  * activation): act[M, I] bf16 = g * sigmoid(beta * g) * (u + 1), g = min(gate, limit), u = clamp(up, +-limit), of the
  * fp32 accumulators; W = [gate rows; up rows].  _decode: 1 <= M <= 128, I % 64 == 0 (weight-streaming kernel);

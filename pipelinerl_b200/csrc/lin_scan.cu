@@ -48,6 +48,7 @@ struct ScanArgs {
   const float* dt_raw; int64_t ld_dt; int off_dt; int groups;
   const float* dt_bias; const float* a_log; const float* skip;
   int vec4;   // every staged vector starts on a 16-byte boundary and dk, dv are multiples of 4: 16-byte cp.async
+  int zero_init;   // the state starts at zero instead of being read (seg_slot may then be null: slot = segment index)
 };
 
 __device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
@@ -82,20 +83,22 @@ __global__ void __launch_bounds__(kThreads) lin_scan_kernel(ScanArgs a) {
   const int dk = a.dk, dv = a.dv;
   const int64_t row0 = a.seg_start[seg];
   const int nv4 = (dv + 3) / 4;                  // state layout: [head][r][column / 4][key lane][column % 4]
-  float* st = a.state + (int64_t)a.seg_slot[seg] * a.state_slot_stride + (int64_t)h * R * nv4 * 32;
+  const int slot = a.seg_slot ? a.seg_slot[seg] : seg;
+  float* st = a.state + (int64_t)slot * a.state_slot_stride + (int64_t)h * R * nv4 * 32;
   const int col0 = vt * kCols + vg * VC;
   float s[R][VC];
 #pragma unroll
   for (int i = 0; i < R; ++i) {
     if constexpr (VC == 4) {        // col0 is a multiple of 4: the thread's four columns are one 16-byte group
       float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (col0 < nv4 * 4) v4 = *reinterpret_cast<const float4*>(st + (((int64_t)i * nv4 + col0 / 4) * kKeyLanes + dg) * 4);
+      if (col0 < nv4 * 4 && !a.zero_init)
+        v4 = *reinterpret_cast<const float4*>(st + (((int64_t)i * nv4 + col0 / 4) * kKeyLanes + dg) * 4);
       s[i][0] = v4.x; s[i][1] = v4.y; s[i][2] = v4.z; s[i][3] = v4.w;
     } else {
 #pragma unroll
       for (int j = 0; j < VC; ++j) {
         const int c = col0 + j;
-        s[i][j] = (c < nv4 * 4) ? st[(((int64_t)i * nv4 + c / 4) * kKeyLanes + dg) * 4 + (c & 3)] : 0.f;
+        s[i][j] = (c < nv4 * 4 && !a.zero_init) ? st[(((int64_t)i * nv4 + c / 4) * kKeyLanes + dg) * 4 + (c & 3)] : 0.f;
       }
     }
   }
@@ -308,6 +311,189 @@ __global__ void gla_decay_kernel(float* __restrict__ z, int64_t ldz, const float
   *p = expf(logsigmoid_f(*p + bias[c]) * inv_tau);
 }
 
+
+// ---- the same recurrences with a long segment cut into pieces that run side by side ---------------------------------
+// A prompt portion of one sequence gives lin_scan_kernel only (value tiles x heads) CTAs, a fraction of a warp per
+// scheduler, and the walk over its tokens is a dependent chain.  The recurrence is linear in the state, so a segment
+// may be cut into pieces of at most kPiece tokens:
+//   1. lin_scan_kernel runs every piece from a ZERO state (pieces are independent: pieces x heads x tiles CTAs); it
+//      writes o_t^local and leaves the piece's own contribution L_c in a scratch state;
+//   2. piece_decay_kernel: D_c[d] = prod of a_t[d] over the piece;
+//   3. carry_kernel walks the pieces of a segment in order, per state element: scratch[c] <- S (the state BEFORE piece
+//      c), S <- D_c * S + L_c; the last S is the sequence's new state;
+//   4. apply_kernel adds what the incoming state contributes: o_t += (q_t * prod_{s <= t in piece} a_s)^T S_before(c),
+//      a [tokens x dk] x [dk x dv] product per piece and head from shared memory.
+// All of it is fp32; the result differs from the token-by-token walk by the rounding of a different summation order.
+constexpr int kPiece = 64;          // tokens per piece at most (the token tile of apply_kernel)
+constexpr int kApplyCols = 64;      // value columns per CTA of apply_kernel
+constexpr int kApplyKeys = 64;      // key channels per round of apply_kernel
+constexpr int kWStride = kPiece + 4;
+
+struct SplitArgs {
+  const int32_t* sub_start; const int32_t* sub_len;     // the pieces (rows of the batch); scratch slot = piece index
+  const int32_t* seg_sub0; const int32_t* seg_nsub;      // first piece and piece count of every segment
+  float* scratch;                                        // [pieces][state_slot_stride]
+  float* cdec;                                           // [pieces][heads][8 r]
+  int r;                                                 // key channels per key lane in the state layout
+};
+
+template <bool SSD>
+__global__ void __launch_bounds__(256) piece_decay_kernel(ScanArgs a, SplitArgs p) {
+  pdl_wait();
+  const int sub = blockIdx.x, h = blockIdx.y, d = threadIdx.x, dpad = kKeyLanes * p.r;
+  if (d >= dpad) return;
+  const int len = p.sub_len[sub];
+  const int64_t row0 = p.sub_start[sub];
+  float prod = 1.f;                    // eight loads in flight at a time; the product keeps the order of the tokens
+  const float neg_a = SSD ? -expf(a.a_log[h]) : 0.f, dtb = SSD ? a.dt_bias[h] : 0.f;
+  if (SSD || d < a.dk) {
+    for (int t0 = 0; t0 < len; t0 += 8) {
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int t = min(t0 + j, len - 1);
+        v[j] = SSD ? a.dt_raw[(row0 + t) * a.ld_dt + a.off_dt + h] : a.avec[(row0 + t) * a.ld_a + h * a.dk + d];
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (t0 + j < len) prod *= SSD ? expf(neg_a * softplus_f(v[j] + dtb)) : v[j];
+    }
+  }
+  p.cdec[((int64_t)sub * a.heads + h) * dpad + d] = prod;
+}
+
+__global__ void __launch_bounds__(256) carry_kernel(ScanArgs a, SplitArgs p) {
+  pdl_wait();
+  const int seg = blockIdx.z, h = blockIdx.y;
+  const int nv4 = (a.dv + 3) / 4, per_head = p.r * nv4 * 32, dpad = kKeyLanes * p.r;
+  const int idx = (blockIdx.x * 256 + threadIdx.x) * 4;          // four columns of one key channel
+  if (idx >= per_head) return;
+  const int d = ((idx / 4) % kKeyLanes) * p.r + idx / (nv4 * 32);
+  const int64_t off = (int64_t)h * per_head + idx;
+  float4* real = reinterpret_cast<float4*>(a.state + (int64_t)a.seg_slot[seg] * a.state_slot_stride + off);
+  float4 s = *real;
+  const int sub0 = p.seg_sub0[seg], nsub = p.seg_nsub[seg];
+  for (int c0 = 0; c0 < nsub; c0 += 8) {       // the loads of eight pieces are in flight together; the chain is arithmetic only
+    float4 loc[8];
+    float dc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int sub = sub0 + min(c0 + j, nsub - 1);
+      dc[j] = p.cdec[((int64_t)sub * a.heads + h) * dpad + d];
+      loc[j] = *reinterpret_cast<const float4*>(p.scratch + (int64_t)sub * a.state_slot_stride + off);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (c0 + j < nsub) {
+        *reinterpret_cast<float4*>(p.scratch + (int64_t)(sub0 + c0 + j) * a.state_slot_stride + off) = s;
+        s = make_float4(fmaf(dc[j], s.x, loc[j].x), fmaf(dc[j], s.y, loc[j].y), fmaf(dc[j], s.z, loc[j].z),
+                        fmaf(dc[j], s.w, loc[j].w));
+      }
+    }
+  }
+  *real = s;
+}
+
+template <bool SSD>
+__global__ void __launch_bounds__(256) apply_kernel(ScanArgs a, SplitArgs p) {
+  pdl_wait();
+  __shared__ __align__(16) float wT[kApplyKeys * kWStride];     // [key channel][token]: q_t[d] * (decay from the piece's start through t)
+  __shared__ __align__(16) float S[kApplyKeys * kApplyCols];    // [key channel][column]: the state before this piece
+  __shared__ float dec[kPiece];
+  const int sub = blockIdx.x, h = blockIdx.y, vt = blockIdx.z, tid = threadIdx.x;
+  const int len = p.sub_len[sub], dk = a.dk, dv = a.dv, r = p.r;
+  const int64_t row0 = p.sub_start[sub];
+  const int grp = SSD ? h / (a.heads / a.groups) : 0;
+  const float* qbase = a.qvec + a.off_q + (SSD ? grp : h) * dk;
+  const int nv4 = (dv + 3) / 4;
+  const float* sc = p.scratch + (int64_t)sub * a.state_slot_stride + (int64_t)h * r * nv4 * 32;
+  const int tx = tid % 16, ty = tid / 16;      // columns 4 tx .., tokens 4 ty ..
+  float acc[4][4] = {};
+  if (SSD) {
+    if (tid < kPiece)
+      dec[tid] = tid < len ? expf(-expf(a.a_log[h]) * softplus_f(a.dt_raw[(row0 + tid) * a.ld_dt + a.off_dt + h] + a.dt_bias[h])) : 1.f;
+    __syncthreads();
+    if (tid == 0) {
+      float cum = 1.f;
+      for (int t = 0; t < kPiece; ++t) { cum *= dec[t]; dec[t] = cum; }
+    }
+    __syncthreads();
+  }
+  // key channels in blocks of kApplyKeys.  Within a block: the decays of the piece, their running product over its
+  // tokens, times q -- every global load independent of the others (a thread per channel walking the tokens would
+  // wait for each load in turn) -- then the state rows of these channels, then the product.
+  for (int d0 = 0; d0 < dk; d0 += kApplyKeys) {
+    const int nd = min(kApplyKeys, dk - d0);
+    if (!SSD) {
+      for (int e = tid; e < kPiece * nd; e += 256) {
+        const int t = e / nd, d = e - t * nd;
+        wT[d * kWStride + t] = t < len ? a.avec[(row0 + t) * a.ld_a + h * dk + d0 + d] : 1.f;
+      }
+      __syncthreads();
+      if (tid < nd) {
+        float cum = 1.f;
+#pragma unroll 16
+        for (int t = 0; t < kPiece; ++t) { cum *= wT[tid * kWStride + t]; wT[tid * kWStride + t] = cum; }
+      }
+      __syncthreads();
+    }
+    for (int e = tid; e < kPiece * nd; e += 256) {
+      const int t = e / nd, d = e - t * nd;
+      const float cum = SSD ? dec[t] : wT[d * kWStride + t];
+      wT[d * kWStride + t] = t < len ? cum * qbase[(row0 + t) * a.ld_q + d0 + d] * a.q_scale : 0.f;
+    }
+    for (int e = tid; e < r * (kApplyCols / 4) * kKeyLanes; e += 256) {      // key lanes fastest: whole 128-byte lines
+      const int dg = e % kKeyLanes, c4 = (e / kKeyLanes) % (kApplyCols / 4), i = e / (kKeyLanes * (kApplyCols / 4));
+      const int d = dg * r + i - d0, col4 = vt * (kApplyCols / 4) + c4;
+      if (d < 0 || d >= nd) continue;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (col4 < nv4) v = *reinterpret_cast<const float4*>(sc + (((int64_t)i * nv4 + col4) * kKeyLanes + dg) * 4);
+      *reinterpret_cast<float4*>(S + d * kApplyCols + c4 * 4) = v;
+    }
+    __syncthreads();
+    if (ty * 4 < len) {
+#pragma unroll 4
+      for (int d = 0; d < nd; ++d) {
+        const float4 w4 = *reinterpret_cast<const float4*>(wT + d * kWStride + ty * 4);
+        const float4 s4 = *reinterpret_cast<const float4*>(S + d * kApplyCols + tx * 4);
+        const float ww[4] = {w4.x, w4.y, w4.z, w4.w}, ss[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(ww[i], ss[j], acc[i][j]);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int t = ty * 4 + i;
+    if (t >= len) break;
+    float* o = a.out + (row0 + t) * a.ld_out + h * dv + vt * kApplyCols + tx * 4;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (vt * kApplyCols + tx * 4 + j < dv) o[j] += acc[i][j];
+  }
+}
+
+template <bool SSD>
+int launch_split(ScanArgs a, int n_seg, SplitArgs p, int n_sub, cudaStream_t st) {
+  p.r = plan_r(a.dk);
+  ScanArgs pieces = a;                 // 1. every piece from a zero state into its scratch slot
+  pieces.seg_start = p.sub_start; pieces.seg_len = p.sub_len; pieces.seg_slot = nullptr;
+  pieces.state = p.scratch; pieces.zero_init = 1;
+  const int rc = launch_scan<SSD>(pieces, n_sub, st);
+  if (rc != PRL_OK) return rc;
+  PRL_CUDA(launch_pdl(piece_decay_kernel<SSD>, dim3(n_sub, a.heads), dim3(256), (size_t)0, st, a, p));
+  PRL_LAUNCH_CHECK();
+  const int nv4 = (a.dv + 3) / 4, per_head = p.r * nv4 * 32;
+  PRL_CUDA(launch_pdl(carry_kernel, dim3((per_head + 1023) / 1024, a.heads, n_seg), dim3(256), (size_t)0, st, a, p));
+  PRL_LAUNCH_CHECK();
+  PRL_CUDA(launch_pdl(apply_kernel<SSD>, dim3(n_sub, a.heads, (a.dv + kApplyCols - 1) / kApplyCols), dim3(256), (size_t)0, st, a, p));
+  PRL_LAUNCH_CHECK();
+  return PRL_OK;
+}
+
 }  // namespace
 }  // namespace prl
 
@@ -325,10 +511,10 @@ extern "C" int prl_gla_decay(float* z, int64_t ldz, const float* bias, float tau
   return PRL_OK;
 }
 
-extern "C" int prl_gla_scan(const float* P, int64_t ldp, int32_t off_q, int32_t off_k, int32_t off_v, float q_scale,
-                            const float* decay, int64_t ld_decay, int32_t heads, int32_t dk, int32_t dv,
-                            const int32_t* seg_start, const int32_t* seg_len, const int32_t* seg_slot, int32_t n_seg,
-                            float* state, float* out, int64_t ld_out, prl_stream_t st) {
+static int gla_scan_impl(const float* P, int64_t ldp, int32_t off_q, int32_t off_k, int32_t off_v, float q_scale,
+                         const float* decay, int64_t ld_decay, int32_t heads, int32_t dk, int32_t dv,
+                         const int32_t* seg_start, const int32_t* seg_len, const int32_t* seg_slot, int32_t n_seg,
+                         float* state, float* out, int64_t ld_out, const SplitArgs* split, int32_t n_sub, prl_stream_t st) {
   PRL_CHECK_ARG(P && decay && seg_start && seg_len && seg_slot && state && out, "prl_gla_scan: NULL argument");
   PRL_CHECK_ARG(heads >= 1 && dk >= 1 && dk <= 256 && dv >= 1 && n_seg >= 1 && n_seg <= 65535,
                 "prl_gla_scan: bad shape (heads=%d dk=%d dv=%d, dk at most 256)", heads, dk, dv);
@@ -342,14 +528,54 @@ extern "C" int prl_gla_scan(const float* P, int64_t ldp, int32_t off_q, int32_t 
   a.avec = decay; a.ld_a = ld_decay;
   a.xval = P; a.ld_x = ldp; a.off_x = off_v;
   a.q_scale = q_scale;
+  if (split) return launch_split<false>(a, n_seg, *split, n_sub, (cudaStream_t)st);
   return launch_scan<false>(a, n_seg, (cudaStream_t)st);
 }
 
-extern "C" int prl_ssd_scan(const float* P, int64_t ldp, int32_t off_dt, const float* xbc, int64_t ld_xbc,
-                            const float* dt_bias, const float* a_log, const float* skip, int32_t heads, int32_t groups,
-                            int32_t n_state, int32_t dv, const int32_t* seg_start, const int32_t* seg_len,
-                            const int32_t* seg_slot, int32_t n_seg, float* state, float* out, int64_t ld_out,
-                            prl_stream_t st) {
+extern "C" int prl_gla_scan(const float* P, int64_t ldp, int32_t off_q, int32_t off_k, int32_t off_v, float q_scale,
+                            const float* decay, int64_t ld_decay, int32_t heads, int32_t dk, int32_t dv,
+                            const int32_t* seg_start, const int32_t* seg_len, const int32_t* seg_slot, int32_t n_seg,
+                            float* state, float* out, int64_t ld_out, prl_stream_t st) {
+  return gla_scan_impl(P, ldp, off_q, off_k, off_v, q_scale, decay, ld_decay, heads, dk, dv, seg_start, seg_len, seg_slot,
+                       n_seg, state, out, ld_out, nullptr, 0, st);
+}
+
+static bool split_args(SplitArgs& p, const int32_t* seg_sub0, const int32_t* seg_nsub, const int32_t* sub_start,
+                       const int32_t* sub_len, int32_t n_sub, float* scratch, float* cdec) {
+  if (!seg_sub0 || !seg_nsub || !sub_start || !sub_len || !scratch || !cdec || n_sub < 1 || n_sub > 65535) return false;
+  if (((uintptr_t)scratch & 15) != 0) return false;
+  p = SplitArgs{};
+  p.seg_sub0 = seg_sub0; p.seg_nsub = seg_nsub; p.sub_start = sub_start; p.sub_len = sub_len;
+  p.scratch = scratch; p.cdec = cdec;
+  return true;
+}
+
+// Floats of the per-piece decay table for one piece (the scratch state of a piece is prl_lin_scan_state_floats).
+extern "C" int64_t prl_lin_scan_piece_decay_floats(int32_t heads, int32_t dk) {
+  if (heads < 1 || dk < 1 || dk > 256) return -1;
+  return (int64_t)heads * kKeyLanes * plan_r(dk);
+}
+extern "C" int32_t prl_lin_scan_piece_tokens() { return kPiece; }
+
+// The same result as prl_gla_scan up to fp32 rounding, with every segment cut into pieces (rows sub_start[i] ..
+// + sub_len[i], at most prl_lin_scan_piece_tokens() each, in order; segment s owns pieces seg_sub0[s] .. + seg_nsub[s])
+// that run side by side.  scratch: [n_sub][prl_lin_scan_state_floats], cdec: [n_sub][prl_lin_scan_piece_decay_floats].
+extern "C" int prl_gla_scan_split(const float* P, int64_t ldp, int32_t off_q, int32_t off_k, int32_t off_v, float q_scale,
+                                  const float* decay, int64_t ld_decay, int32_t heads, int32_t dk, int32_t dv,
+                                  const int32_t* seg_slot, int32_t n_seg, const int32_t* seg_sub0, const int32_t* seg_nsub,
+                                  const int32_t* sub_start, const int32_t* sub_len, int32_t n_sub, float* scratch,
+                                  float* cdec, float* state, float* out, int64_t ld_out, prl_stream_t st) {
+  SplitArgs p;
+  PRL_CHECK_ARG(split_args(p, seg_sub0, seg_nsub, sub_start, sub_len, n_sub, scratch, cdec), "prl_gla_scan_split: bad piece tables");
+  return gla_scan_impl(P, ldp, off_q, off_k, off_v, q_scale, decay, ld_decay, heads, dk, dv, sub_start, sub_len, seg_slot,
+                       n_seg, state, out, ld_out, &p, n_sub, st);
+}
+
+static int ssd_scan_impl(const float* P, int64_t ldp, int32_t off_dt, const float* xbc, int64_t ld_xbc,
+                         const float* dt_bias, const float* a_log, const float* skip, int32_t heads, int32_t groups,
+                         int32_t n_state, int32_t dv, const int32_t* seg_start, const int32_t* seg_len,
+                         const int32_t* seg_slot, int32_t n_seg, float* state, float* out, int64_t ld_out,
+                         const SplitArgs* split, int32_t n_sub, prl_stream_t st) {
   PRL_CHECK_ARG(P && xbc && dt_bias && a_log && skip && seg_start && seg_len && seg_slot && state && out,
                 "prl_ssd_scan: NULL argument");
   PRL_CHECK_ARG(heads >= 1 && groups >= 1 && heads % groups == 0 && n_state >= 1 && n_state <= 256 && dv >= 1 &&
@@ -367,5 +593,27 @@ extern "C" int prl_ssd_scan(const float* P, int64_t ldp, int32_t off_dt, const f
   a.q_scale = 1.f;
   a.dt_raw = P; a.ld_dt = ldp; a.off_dt = off_dt; a.groups = groups;
   a.dt_bias = dt_bias; a.a_log = a_log; a.skip = skip;
+  if (split) return launch_split<true>(a, n_seg, *split, n_sub, (cudaStream_t)st);
   return launch_scan<true>(a, n_seg, (cudaStream_t)st);
+}
+
+extern "C" int prl_ssd_scan(const float* P, int64_t ldp, int32_t off_dt, const float* xbc, int64_t ld_xbc,
+                            const float* dt_bias, const float* a_log, const float* skip, int32_t heads, int32_t groups,
+                            int32_t n_state, int32_t dv, const int32_t* seg_start, const int32_t* seg_len,
+                            const int32_t* seg_slot, int32_t n_seg, float* state, float* out, int64_t ld_out,
+                            prl_stream_t st) {
+  return ssd_scan_impl(P, ldp, off_dt, xbc, ld_xbc, dt_bias, a_log, skip, heads, groups, n_state, dv, seg_start, seg_len,
+                       seg_slot, n_seg, state, out, ld_out, nullptr, 0, st);
+}
+
+extern "C" int prl_ssd_scan_split(const float* P, int64_t ldp, int32_t off_dt, const float* xbc, int64_t ld_xbc,
+                                  const float* dt_bias, const float* a_log, const float* skip, int32_t heads, int32_t groups,
+                                  int32_t n_state, int32_t dv, const int32_t* seg_slot, int32_t n_seg,
+                                  const int32_t* seg_sub0, const int32_t* seg_nsub, const int32_t* sub_start,
+                                  const int32_t* sub_len, int32_t n_sub, float* scratch, float* cdec, float* state,
+                                  float* out, int64_t ld_out, prl_stream_t st) {
+  SplitArgs p;
+  PRL_CHECK_ARG(split_args(p, seg_sub0, seg_nsub, sub_start, sub_len, n_sub, scratch, cdec), "prl_ssd_scan_split: bad piece tables");
+  return ssd_scan_impl(P, ldp, off_dt, xbc, ld_xbc, dt_bias, a_log, skip, heads, groups, n_state, dv, sub_start, sub_len,
+                       seg_slot, n_seg, state, out, ld_out, &p, n_sub, st);
 }

@@ -267,7 +267,7 @@ class HybridConfig:
 class _Rows:
     """Activation buffers and ragged-row metadata for up to `n` rows."""
 
-    def __init__(self, eng: "HybridEngine", n: int):
+    def __init__(self, eng: "HybridEngine", n: int, pieces: bool = False):
         cfg, d, T = eng.cfg, eng.dev, eng.op_dtype
         W = cfg.width
         wide_p, wide_aux, wide_o, wide_o2, wide_q, wide_f = W, 1, 1, 1, 1, 1
@@ -308,6 +308,21 @@ class _Rows:
         self.row_back = torch.zeros(n, **i32)
         self.seg = torch.zeros(4, n, **i32)                     # seg_start, seg_len, seg_pos0, seg_slot
         self.want = torch.zeros(n, **i32)
+        # side-by-side pieces of long segments (prompt portions only): piece tables, a scratch state and a decay
+        # table per piece, sized for the largest recurrence of the model
+        self.n_sub, self.max_sub = 0, 0
+        if pieces:
+            lib, st, dc = eng.lib, 1, 1
+            for L in cfg.layers:
+                for heads, dk, dv in ([(L.gla.heads, L.gla.dim, L.gla.vdim)] if L.kind == "gla" else
+                                      [(L.ssd.heads, L.ssd.state, L.ssd.vdim)]):
+                    st = max(st, int(lib.prl_lin_scan_state_floats(heads, dk, dv)))
+                    dc = max(dc, int(lib.prl_lin_scan_piece_decay_floats(heads, dk)))
+            self.max_sub = n // eng.piece_tokens + 8
+            self.scratch = torch.zeros(self.max_sub * st, **f32)
+            self.cdec = torch.zeros(self.max_sub * dc, **f32)
+            self.sub = torch.zeros(2, self.max_sub, **i32)          # sub_start, sub_len
+            self.seg_sub = torch.zeros(2, n, **i32)                 # first piece, piece count of every segment
 
 
 class HybridEngine(EngineCore):
@@ -321,6 +336,12 @@ class HybridEngine(EngineCore):
         self.force_plain_gemm = False      # tests: route every GEMM through the CUDA-core kernel
         self.unfused_glu = False           # tests: gate_up GEMM + activation kernel instead of the GEMM's gated epilogue
         self.force_plain_attn = False      # tests: the any-geometry attention kernel also where the tcgen05 ones fit
+        # Long prompt portions run their recurrences as side-by-side pieces (prl_*_scan_split): same values up to fp32
+        # rounding, many times the parallelism.  Off in the true-fp32 mode, whose results do not depend on the cut of
+        # a prompt bit for bit.  A batch qualifies when its longest segment has split_min_rows rows.
+        self.split_scan = not self.f32
+        self.split_min_rows = 256
+        self.piece_tokens = 64             # tokens per piece (tests lower it); at most prl_lin_scan_piece_tokens()
         self._rows: _Rows | None = None
         super().__init__(cfg, arena, **kw)
 
@@ -404,6 +425,10 @@ class HybridEngine(EngineCore):
         W, eps, vec = cfg.width, cfg.eps, self.vec
         seg_start, seg_len, seg_slot = R.seg[0].data_ptr(), R.seg[1].data_ptr(), R.seg[3].data_ptr()
         P, x, xa = R.P.data_ptr(), R.x.data_ptr(), R.xa.data_ptr()
+        n_sub = 0 if decode else R.n_sub
+        if n_sub:
+            pieces = (R.seg_sub[0].data_ptr(), R.seg_sub[1].data_ptr(), R.sub[0].data_ptr(), R.sub[1].data_ptr(), n_sub,
+                      R.scratch.data_ptr(), R.cdec.data_ptr())
         for i, L in enumerate(cfg.layers):
             w = f"l{L.weights_of}."
             if L.kind == "gla":
@@ -415,9 +440,14 @@ class HybridEngine(EngineCore):
                 _lib.check(lib.prl_gemm_any(P + 4 * (2 * nq + 2 * nv), 1, ld, self.arena.ptr(w + "mix.a2"), f32, g.rank,
                                             n, nq, g.rank, R.aux.data_ptr(), nq, st))
                 _lib.check(lib.prl_gla_decay(R.aux.data_ptr(), nq, vec[w + "mix.a2.b"].data_ptr(), g.tau, n, nq, st))
-                _lib.check(lib.prl_gla_scan(P, ld, 0, nq, 2 * nq, g.dim ** -0.5, R.aux.data_ptr(), nq, g.heads, g.dim, g.vdim,
-                                            seg_start, seg_len, seg_slot, ns, self.gla_state[i].data_ptr(), R.o.data_ptr(),
-                                            nv, st))
+                if n_sub:
+                    _lib.check(lib.prl_gla_scan_split(P, ld, 0, nq, 2 * nq, g.dim ** -0.5, R.aux.data_ptr(), nq, g.heads, g.dim,
+                                                      g.vdim, seg_slot, ns, *pieces, self.gla_state[i].data_ptr(),
+                                                      R.o.data_ptr(), nv, st))
+                else:
+                    _lib.check(lib.prl_gla_scan(P, ld, 0, nq, 2 * nq, g.dim ** -0.5, R.aux.data_ptr(), nq, g.heads, g.dim,
+                                                g.vdim, seg_start, seg_len, seg_slot, ns, self.gla_state[i].data_ptr(),
+                                                R.o.data_ptr(), nv, st))
                 _lib.check(lib.prl_gate_norm(R.o.data_ptr(), 1, nv, P + 4 * (2 * nq + nv), ld, vec[w + "mix.norm"].data_ptr(),
                                              g.vdim, g.vdim, n, nv, 0, 0, 1, eps, R.ya.data_ptr(), f32, st))
                 k0 = self._mm(R.ya, nv, w + "mix.o", W, R.y0, n, split=True)
@@ -466,11 +496,16 @@ class HybridEngine(EngineCore):
                                              R.row_back.data_ptr(), self.conv_state[i].data_ptr(), R.aux.data_ptr(), st))
                 _lib.check(lib.prl_conv_state_update(P, ld, left + inner, ch, s.conv, seg_start, seg_len, seg_slot, ns,
                                                      self.conv_state[i].data_ptr(), st))
-                _lib.check(lib.prl_ssd_scan(P, ld, left + inner + ch, R.aux.data_ptr(), ch,
-                                            vec[w + "mix.right.dt_bias"].data_ptr(), vec[w + "mix.right.A_log"].data_ptr(),
-                                            vec[w + "mix.right.D"].data_ptr(), s.heads, s.groups, s.state, s.vdim,
-                                            seg_start, seg_len, seg_slot, ns, self.ssd_state[i].data_ptr(),
-                                            R.o2.data_ptr(), inner, st))
+                ssd_vec = (vec[w + "mix.right.dt_bias"].data_ptr(), vec[w + "mix.right.A_log"].data_ptr(),
+                           vec[w + "mix.right.D"].data_ptr())
+                if n_sub:
+                    _lib.check(lib.prl_ssd_scan_split(P, ld, left + inner + ch, R.aux.data_ptr(), ch, *ssd_vec, s.heads,
+                                                      s.groups, s.state, s.vdim, seg_slot, ns, *pieces,
+                                                      self.ssd_state[i].data_ptr(), R.o2.data_ptr(), inner, st))
+                else:
+                    _lib.check(lib.prl_ssd_scan(P, ld, left + inner + ch, R.aux.data_ptr(), ch, *ssd_vec, s.heads, s.groups,
+                                                s.state, s.vdim, seg_start, seg_len, seg_slot, ns,
+                                                self.ssd_state[i].data_ptr(), R.o2.data_ptr(), inner, st))
                 _lib.check(lib.prl_gate_norm(R.o2.data_ptr(), 1, inner, P + 4 * left, ld, vec[w + "mix.right.norm"].data_ptr(),
                                              inner, inner // s.norm_groups, n, inner, 0, 1, 1, eps, R.yb.data_ptr(), f32, st))
                 k1 = self._mm(R.yb, inner, w + "mix.right.o", W, R.y1, n, split=True)
@@ -511,7 +546,7 @@ class HybridEngine(EngineCore):
     def _forward_rows(self, segs, want_rows, trace=None):
         cfg, lib = self.cfg, self.lib
         if self._rows is None:
-            self._rows = _Rows(self, max(self.prefill_chunk, 1))
+            self._rows = _Rows(self, max(self.prefill_chunk, 1), pieces=True)
         R = self._rows
         n = sum(k for _, _, k in segs)
         if n > R.n:
@@ -527,6 +562,19 @@ class HybridEngine(EngineCore):
             at += k
         ns = len(segs)
         i32 = torch.int32
+        R.n_sub = 0
+        if self.split_scan and max(k for _, _, k in segs) >= self.split_min_rows:
+            step = min(self.piece_tokens, int(lib.prl_lin_scan_piece_tokens()))
+            sub, seg_sub = [[], []], [[], []]
+            for start, k in zip(meta[0], meta[1]):
+                seg_sub[0].append(len(sub[0]))
+                seg_sub[1].append((k + step - 1) // step)
+                sub[0] += range(start, start + k, step)
+                sub[1] += [min(step, k - c) for c in range(0, k, step)]
+            if len(sub[0]) <= R.max_sub:          # else: many short segments beside the long one, walk them token by token
+                R.n_sub = len(sub[0])
+                R.sub[:, :R.n_sub].copy_(torch.tensor(sub, dtype=i32), non_blocking=True)
+                R.seg_sub[:, :ns].copy_(torch.tensor(seg_sub, dtype=i32), non_blocking=True)
         R.tokens[:n].copy_(torch.tensor(toks, dtype=i32), non_blocking=True)
         R.row_pos[:n].copy_(torch.tensor(pos, dtype=i32), non_blocking=True)
         R.row_slot[:n].copy_(torch.tensor(slot, dtype=i32), non_blocking=True)

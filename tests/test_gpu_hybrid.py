@@ -179,6 +179,42 @@ def test_long_memory_of_the_recurrent_states(cuda_device):
     assert hc.rel_err(hc.stream_logits(eng, toks, [7, 2, 120, 2, 9]), ref) < F32_TOL      # then 160 single tokens
 
 
+@pytest.mark.parametrize("piece", [16, 64])
+def test_long_portions_as_side_by_side_pieces(cuda_device, piece):
+    """The recurrences of a long portion cut into pieces that are scanned from a zero state, chained, and corrected by
+    the incoming state's share (prl_gla_scan_split / prl_ssd_scan_split), in fp32 against the oracle: pieces that end
+    inside a portion, a ragged last piece, portions below the threshold walking token by token from the state the
+    pieces left (and the other way round), several long segments in one batch, and decays close to 1 so that the
+    first tokens still matter hundreds of tokens and many pieces later."""
+    config = hc.model([hc.gla_layer(tau=8.0, mlp=hc.dense()), hc.par_layer(mlp=hc.dense(ff=48)),
+                       hc.shared(hc.gla_layer(tau=8.0, mlp=hc.dense()), 0),
+                       hc.par_layer(heads=2, kv_heads=1, dim=12, vdim=8, rot=4, conv=2, groups=1, norm_groups=1, s_heads=2,
+                                    s_vdim=16, state=20)], vocab=80, width=64)
+    wt = _weights(config, 21)
+    wt["l0.mix.a2.b"] += 4.0
+    wt["l1.mix.right.dt_bias"] -= 3.0
+    toks = hc.tokens_for(config, 300, seed=9)
+    ref = hc.oracle_logits(config, wt, toks)
+    from oracle import hybrid_oracle as ho
+    assert hc.rel_err(ho.forward(config, wt, toks[1:])[250:], ref[251:]) > 50 * F32_TOL   # token 0 still matters at 250+
+    eng = hc.build_engine(config, wt, torch.float32, cuda_device, prefill_chunk=256)
+    eng.split_scan, eng.split_min_rows, eng.piece_tokens = True, 40, piece
+    for portions in ([300], [41, 2, 130, 3, 100], [1, 255, 39, 2]):
+        assert hc.rel_err(hc.stream_logits(eng, toks, portions), ref) < F32_TOL
+    assert eng._rows.n_sub == 0                       # the last batches were single tokens: no pieces
+    a, b, c = eng.open_stream(), eng.open_stream(), eng.open_stream()
+    other = hc.tokens_for(config, 75, seed=10)
+    eng.feed([(c, toks[:5], [])])
+    got = eng.feed([(a, toks[:100], list(range(100))), (c, toks[5:6], [0]), (b, other, list(range(75)))]).double().cpu()
+    assert eng._rows.n_sub == -(-100 // piece) + 1 + -(-75 // piece)
+    assert hc.rel_err(got[:100], ref[:100]) < F32_TOL and hc.rel_err(got[100:101], ref[5:6]) < F32_TOL
+    assert hc.rel_err(got[101:], hc.oracle_logits(config, wt, other)) < F32_TOL
+    got = eng.feed([(a, toks[100:190], list(range(90))), (b, toks[:1], [])]).double().cpu()      # pieces continue a state
+    assert hc.rel_err(got, ref[100:190]) < F32_TOL
+    for s in (a, b, c):
+        eng.close_stream(s)
+
+
 def test_first_tokens_and_one_token_sequences(cuda_device):
     wt = _weights(FULL, 12)
     eng = hc.build_engine(FULL, wt, torch.float32, cuda_device)

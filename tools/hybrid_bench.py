@@ -135,7 +135,7 @@ def kernel_table(eng, s, batch, chunk, timer):
     out = {}
     i32 = dict(dtype=torch.int32, device=eng.dev)
     for shape, n, ns in (("decode", batch, batch), ("prefill", chunk, 1)):
-        R = _Rows(eng, n)
+        R = _Rows(eng, n, pieces=shape == "prefill")
         R.P.normal_(0, 0.5)
         R.aux.uniform_(0.9, 1.0)                           # decays (GLA) / convolved inputs (state-space)
         if shape == "decode":
@@ -144,6 +144,13 @@ def kernel_table(eng, s, batch, chunk, timer):
         else:
             R.seg[:, :1].copy_(torch.tensor([[0], [n], [0], [0]], **i32))
             R.row_slot.zero_(); R.row_pos.copy_(torch.arange(n, **i32)); R.row_back.copy_(torch.arange(n, **i32))
+            step = eng.piece_tokens                            # the one segment as side-by-side pieces
+            n_sub = (n + step - 1) // step
+            R.sub[0, :n_sub].copy_(torch.arange(0, n, step, **i32))
+            R.sub[1, :n_sub].copy_(torch.tensor([min(step, n - c) for c in range(0, n, step)], **i32))
+            R.seg_sub[:, :1].copy_(torch.tensor([[0], [n_sub]], **i32))
+            pieces = (R.seg_sub[0].data_ptr(), R.seg_sub[1].data_ptr(), R.sub[0].data_ptr(), R.sub[1].data_ptr(), n_sub,
+                      R.scratch.data_ptr(), R.cdec.data_ptr())
         seg = [R.seg[k].data_ptr() for k in range(4)]
         vec = eng.vec
         nq, nv = g.heads * g.dim, g.heads * g.vdim
@@ -159,6 +166,14 @@ def kernel_table(eng, s, batch, chunk, timer):
         flops = 5.0 * n * g.heads * g.dim * g.vdim
         out[f"gla_scan/{shape}"] = dict(ms=round(ms, 4), hbm_frac=round((state_b + io_b) / ms / 1e6 / hbm, 3),
                                         fp32_fma_frac=round(flops / ms / 1e9 / fma_tflops, 3))
+        if shape == "prefill":
+            def gla_split():
+                _lib.check(lib.prl_gla_scan_split(R.P.data_ptr(), ldg, 0, nq, 2 * nq, g.dim ** -0.5, R.aux.data_ptr(), nq, g.heads,
+                                                  g.dim, g.vdim, seg[3], ns, *pieces, eng.gla_state[gi].data_ptr(),
+                                                  R.o.data_ptr(), nv, st))
+            ms = timer.events(gla_split)
+            out["gla_scan_split/prefill"] = dict(ms=round(ms, 4), hbm_frac=round((state_b * (1 + 2 * n_sub) + io_b) / ms / 1e6 / hbm, 3),
+                                                 fp32_fma_frac=round(1.4 * flops / ms / 1e9 / fma_tflops, 3))
         wp = f"l{par.weights_of}."
         left = a.heads * a.dim + a.kv_heads * (a.dim + a.vdim) + a.heads * a.vdim
         ldp, inner, ch = left + ss.in_rows, ss.inner, ss.conv_channels
@@ -174,6 +189,16 @@ def kernel_table(eng, s, batch, chunk, timer):
         flops = 5.0 * n * ss.heads * ss.state * ss.vdim
         out[f"ssd_scan/{shape}"] = dict(ms=round(ms, 4), hbm_frac=round((state_b + io_b) / ms / 1e6 / hbm, 3),
                                         fp32_fma_frac=round(flops / ms / 1e9 / fma_tflops, 3))
+
+        if shape == "prefill":
+            def ssd_split():
+                _lib.check(lib.prl_ssd_scan_split(R.P.data_ptr(), ldp, left + inner + ch, R.aux.data_ptr(), ch,
+                                                  vec[wp + "mix.right.dt_bias"].data_ptr(), vec[wp + "mix.right.A_log"].data_ptr(),
+                                                  vec[wp + "mix.right.D"].data_ptr(), ss.heads, ss.groups, ss.state, ss.vdim,
+                                                  seg[3], ns, *pieces, eng.ssd_state[pi].data_ptr(), R.o2.data_ptr(), inner, st))
+            ms = timer.events(ssd_split)
+            out["ssd_scan_split/prefill"] = dict(ms=round(ms, 4), hbm_frac=round((state_b * (1 + 2 * n_sub) + io_b) / ms / 1e6 / hbm, 3),
+                                                 fp32_fma_frac=round(1.4 * flops / ms / 1e9 / fma_tflops, 3))
 
         def conv():
             _lib.check(lib.prl_conv_silu(R.P.data_ptr(), ldp, left + inner, n, ch, ss.conv, vec[wp + "mix.right.conv"].data_ptr(),
