@@ -141,8 +141,9 @@ class HybridConfig:
                                                               float(m["tau"]), int(rank)), mlp=mlp))
             elif L["type"] == "parallel":
                 a, s = m["left"], m["right"]
-                attn = AttnSpec(int(a["heads"]), int(a["kv_heads"]), int(a["dim"]), int(a["vdim"]),
-                                int(a["rot"]["dims"]), float(a["rot"]["base"]), float(a["scale"]))
+                rot = a.get("rot") or {}                       # no rotary block: no dimension is rotated
+                attn = AttnSpec(int(a["heads"]), int(a.get("kv_heads", a["heads"])), int(a["dim"]), int(a.get("vdim", a["dim"])),
+                                int(rot.get("dims", 0)), float(rot.get("base", 10000.0)), float(a["scale"]))
                 ssd = SsdSpec(int(s["heads"]), int(s["vdim"]), int(s["state"]), int(s["groups"]), int(s["conv"]),
                               int(s["norm_groups"]))
                 layers.append(LayerSpec("parallel", j, attn=attn, ssd=ssd, left_scale=float(m["left_scale"]),
