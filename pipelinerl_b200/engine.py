@@ -486,7 +486,7 @@ class EngineCore:
                 want.append(at + w)
             segs.append((req, s0, len(toks)))
             at += len(toks)
-        out, C, base = [], self.prefill_chunk, 0
+        out, order, C, base = [], [], self.prefill_chunk, 0
         while segs:                                  # batches of at most prefill_chunk rows; a long portion is cut
             batch, room = [], C
             while segs and room:
@@ -499,16 +499,23 @@ class EngineCore:
                 else:
                     segs[0] = (req, s0 + take, k - take)
             rows = C - room
-            w_here = [w - base for w in want if base <= w < base + rows]
+            here = [i for i, w in enumerate(want) if base <= w < base + rows]
+            w_here = [want[i] - base for i in here]
             lg = self._forward_rows(batch, w_here)
             if w_here:
                 out.append(lg)
+                order += here
             for req, s0, take in batch:
                 req.prefilled = s0 + take
             base += rows
         if not out:
             return None
-        return out[0] if len(out) == 1 else torch.cat(out)
+        lg = out[0] if len(out) == 1 else torch.cat(out)
+        if order != sorted(order):                   # unsorted indices of a portion that was cut: back to the caller's order
+            back = torch.empty(len(order), dtype=torch.long)
+            back[torch.tensor(order)] = torch.arange(len(order))
+            lg = lg[back.to(lg.device)]
+        return lg
 
     def close_stream(self, req: Request) -> None:
         if self.stream_req.pop(req.slot, None) is not req:

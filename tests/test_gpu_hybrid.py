@@ -90,6 +90,21 @@ def test_portions_of_several_sizes(cuda_device, portions):
     assert hc.rel_err(hc.stream_logits(eng, toks, portions), ref) < F32_TOL
 
 
+def test_wanted_rows_come_back_in_the_order_asked_for(cuda_device):
+    """A portion that the engine cuts (96-row batches) with wanted places out of order, beside a second stream."""
+    wt = _weights(FULL, 4)
+    toks, other = hc.tokens_for(FULL, 140, seed=6), hc.tokens_for(FULL, 9, seed=8)
+    eng = hc.build_engine(FULL, wt, torch.float32, cuda_device, prefill_chunk=96)
+    every = hc.stream_logits(eng, toks, [140])
+    alone = hc.stream_logits(eng, other, [9])
+    a, b = eng.open_stream(), eng.open_stream()
+    asked = [139, 0, 97, 95, 96, 3]
+    got = eng.feed([(a, toks, asked), (b, other, [8, 2])]).double().cpu()
+    eng.close_stream(a), eng.close_stream(b)
+    assert got.shape[0] == 8
+    assert hc.rel_err(got[:6], every[asked]) < F32_TOL and hc.rel_err(got[6:], alone[[8, 2]]) < F32_TOL
+
+
 def test_unequal_batches_equal_each_request_alone(cuda_device):
     wt = _weights(FULL, 7)
     seqs = [hc.tokens_for(FULL, n, seed=10 + n) for n in (1, 37, 130, 66)]
