@@ -119,31 +119,46 @@ __global__ void rmsnorm_rows_kernel(const float* __restrict__ x, const int32_t* 
 template <typename T, typename TO>
 __global__ void gate_norm_kernel(const TO* __restrict__ o, int64_t ldo, const float* __restrict__ g, int64_t ldg,
                                  const float* __restrict__ gain, int gain_period, int gs, int C, int act_sigmoid,
-                                 int gate_first, int norm, float eps, T* __restrict__ out) {
+                                 int gate_first, int norm, float eps, int keep, T* __restrict__ out) {
   pdl_wait();   // launched with the programmatic-serialization attribute like the engine's other step kernels; no early
                 // trigger: letting the next grid become resident early measured +3 ms on a 4096-token prefill and +-0 on decode
+  extern __shared__ float kept[];    // [2][gs]: the values to be normed and the gates between the two passes (keep)
   __shared__ float red[32];
   const int r = blockIdx.x, c0 = blockIdx.y * gs;
+  const float* gr = g + (int64_t)r * ldg + c0;
+  const int64_t ro = (int64_t)r * ldo + c0;
   float inv = 1.f;
   if (norm) {
     float ss = 0.f;
+#pragma unroll 4
     for (int j = threadIdx.x; j < gs; j += blockDim.x) {
-      float v = ldf(o, (int64_t)r * ldo + c0 + j);
-      if (gate_first) {
-        const float z = g[(int64_t)r * ldg + c0 + j];
-        v *= act_sigmoid ? sigmoid_f(z) : silu_f(z);
+      float v = ldf(o, ro + j);
+      if (gate_first || keep) {
+        const float z = gr[j];
+        const float a = act_sigmoid ? sigmoid_f(z) : silu_f(z);
+        if (gate_first) v *= a;
+        if (keep) { kept[j] = v; kept[gs + j] = a; }      // read back by the same thread
       }
       ss += v * v;
     }
     ss = block_sum(ss, red);
     inv = 1.f / sqrtf(ss / (float)gs + eps);
   }
+  const bool kept_here = norm && keep;
+#pragma unroll 4
   for (int j = threadIdx.x; j < gs; j += blockDim.x) {
     const int c = c0 + j;
-    const float z = g[(int64_t)r * ldg + c];
-    const float a = act_sigmoid ? sigmoid_f(z) : silu_f(z);
-    float v = ldf(o, (int64_t)r * ldo + c);
-    if (norm) v = gate_first ? (v * a) * inv * gain[c % gain_period] : v * inv * gain[c % gain_period] * a;
+    float a, v;
+    if (kept_here) {
+      v = kept[j];
+      a = kept[gs + j];
+    } else {
+      const float z = gr[j];
+      a = act_sigmoid ? sigmoid_f(z) : silu_f(z);
+      v = ldf(o, ro + j);
+      if (norm && gate_first) v *= a;
+    }
+    if (norm) v = gate_first ? v * inv * gain[c % gain_period] : v * inv * gain[c % gain_period] * a;
     else v = v * a;
     stf(out, (int64_t)r * C + c, v);
   }
@@ -340,10 +355,14 @@ extern "C" int prl_gate_norm(const void* o, int32_t o_f32, int64_t ldo, const fl
                 "prl_gate_norm: bad argument (C=%d group=%d)", C, group_size);
   PRL_CHECK_ARG(!norm || (gain && gain_period >= 1), "prl_gate_norm: a norm needs its gain");
   dim3 grid(n, C / group_size);
-  const int th = row_threads(group_size);
+  int th = ((group_size + 31) / 32) * 32;
+  const int cap = (int64_t)n * (C / group_size) <= 512 ? 1024 : 256;   // few blocks: more threads per group; many: more groups per SM
+  th = th > cap ? cap : th;
+  const int keep = norm && 2 * (size_t)group_size * sizeof(float) <= 40 * 1024 ? 1 : 0;
+  const size_t smem = keep ? 2 * (size_t)group_size * sizeof(float) : 0;
   cudaStream_t s = (cudaStream_t)st;
-#define PRL_GN(T, TO) PRL_CUDA(launch_pdl((gate_norm_kernel<T, TO>), dim3(grid), dim3(th), (size_t)(0), s, (const TO*)o, ldo, g, ldg, gain, gain_period, group_size, C, \
-                                                                   act_sigmoid, gate_first, norm, eps, (T*)out))
+#define PRL_GN(T, TO) PRL_CUDA(launch_pdl((gate_norm_kernel<T, TO>), dim3(grid), dim3(th), smem, s, (const TO*)o, ldo, g, ldg, gain, gain_period, group_size, C, \
+                                                                   act_sigmoid, gate_first, norm, eps, keep, (T*)out))
   if (f32) { if (o_f32) PRL_GN(float, float); else PRL_GN(float, bf16); }
   else { if (o_f32) PRL_GN(bf16, float); else PRL_GN(bf16, bf16); }
 #undef PRL_GN
