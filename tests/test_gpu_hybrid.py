@@ -33,6 +33,9 @@ MECHANISMS = {
     "state_space_one_group_taps5": hc.model([hc.par_layer(left_scale=0.0, right_scale=1.0, s_heads=3, s_vdim=20, state=9, groups=1,
                                                           conv=5, norm_groups=1)]),
     "state_space_taps1": hc.model([hc.par_layer(left_scale=0.0, right_scale=1.0, conv=1, norm_groups=4, groups=4)]),
+    # one norm group of 5632 channels: wider than what the gate-and-norm kernel keeps in shared memory between its passes
+    "state_space_wide_norm_group": hc.model([hc.par_layer(left_scale=0.0, right_scale=1.0, s_heads=44, s_vdim=128, state=8,
+                                                          groups=1, norm_groups=1)]),
     "feed_forward": hc.model([hc.gla_layer(mlp=hc.dense())]),
     "parallel_both": hc.model([hc.par_layer(mlp=hc.dense(ff=40, limit=0.5))]),
 }
