@@ -666,6 +666,72 @@ int prl_gemm_glu_clamped_f32(const void* X_bf16, int64_t ldx, const void* W_gate
 /* decode step: per-slot engine state -> ragged-row metadata (seg_len = active, row_slot = slot or -1) */
 int prl_decode_rows(const uint8_t* active, int32_t B, int32_t* seg_len, int32_t* row_slot, prl_stream_t stream);
 
+/* ---- further mixers, norms and feed-forwards of the hybrid family (csrc/hybrid_ops.cu, attn_any.cu, lin_scan.cu,
+ * moe_ops.cu) ---- */
+/* x = embed[token] * scale + sinusoid(pos): channel 2i sin(pos * freq[i]), channel 2i+1 cos; x0a (nullable): a second
+ * operand-type copy of the result */
+int prl_embed_sinusoid(const int32_t* tokens, const void* embed, int32_t f32, float scale, const double* freq,
+                       const int32_t* row_pos, int32_t n, int32_t W, int32_t vocab, float* x, void* xa, void* x0a,
+                       prl_stream_t stream);
+/* out[n, 2W] = [a | b] */
+int prl_concat_rows(const void* a, const void* b, int32_t n, int32_t W, void* out, int32_t f32, prl_stream_t stream);
+/* v = s0 norm_g0(y0) + s1 norm_g1(y1); v = norm_post(v); x = (add ? x : 0) + v + bias; xa = T(norm_next(x)); every
+ * norm is skipped when its gain is NULL; y_i may be n_split_i slices [slice][n][ld] that are summed first */
+int prl_sublayer_close(const float* y0, int64_t ld0, int32_t n_split0, const float* gain0, float s0, const float* y1,
+                       int64_t ld1, int32_t n_split1, const float* gain1, float s1, const float* post_gain,
+                       const float* bias, int32_t add, const float* next_gain, float eps, int32_t n, int32_t W, float* x,
+                       void* xa, int32_t f32, prl_stream_t stream);
+/* attention front end with per-head unit norms (biases and gains nullable); off_v < 0: the value is the key as
+ * projected (with its bias, before its norm) */
+int prl_qk_headnorm_cache(const float* P, int64_t ldp, int32_t off_q, int32_t off_k, int32_t off_v, int32_t n, int32_t H,
+                          int32_t G, int32_t dim, int32_t vdim, const float* q_bias, const float* k_bias,
+                          const float* q_gain, const float* k_gain, float eps, const int32_t* row_pos,
+                          const int32_t* row_slot, const int32_t* block_table, int32_t max_blocks, int32_t page_size,
+                          void* q_out, void* k_pool, void* v_pool, int32_t f32, prl_stream_t stream);
+/* prl_attn_any with a sliding window (0: none) that keeps the first keep_first tokens, a tanh cap on the scores (0:
+ * none), and the output in fp32 or (out_is_t) in the cache's element type */
+int prl_attn_any_masked(const void* q, const void* k_pool, const void* v_pool, int32_t f32, const int32_t* block_table,
+                        int32_t max_blocks, int32_t page_size, const int32_t* seg_start, const int32_t* seg_len,
+                        const int32_t* seg_pos0, const int32_t* seg_slot, int32_t n_seg, int32_t max_q, int32_t H,
+                        int32_t G, int32_t dim, int32_t vdim, float scale, int32_t window, int32_t keep_first,
+                        float softcap, int32_t out_is_t, void* out, prl_stream_t stream);
+/* in-place SiLU of columns off .. off + C of P (act = 0); out = T(relu(P)^2) (act = 0) */
+int prl_act_cols(float* P, int64_t ld, int32_t off, int32_t n, int32_t C, int32_t act, prl_stream_t stream);
+int prl_act_store(const float* P, int64_t ld, int32_t n, int32_t F, int32_t act, void* out, int32_t f32,
+                  prl_stream_t stream);
+/* S_t = a_t S_(t-1) + b_t k_t v_t^T, o_t = q_scale S_t^T q_t with one (a_t, b_t) per head and token: gates[row * ld_g +
+ * off_g + 2 head + {0, 1}], or (gates NULL) a_t = const_decay[head], b_t = 1 */
+int prl_decay_scan(const float* P, int64_t ldp, int32_t off_q, int32_t off_k, float q_scale, const float* xval,
+                   int64_t ld_x, int32_t off_x, const float* gates, int64_t ld_g, int32_t off_g,
+                   const float* const_decay, int32_t heads, int32_t dk, int32_t dv, const int32_t* seg_start,
+                   const int32_t* seg_len, const int32_t* seg_slot, int32_t n_seg, float* state, float* out,
+                   int64_t ld_out, prl_stream_t stream);
+int prl_decay_scan_split(const float* P, int64_t ldp, int32_t off_q, int32_t off_k, float q_scale, const float* xval,
+                         int64_t ld_x, int32_t off_x, const float* gates, int64_t ld_g, int32_t off_g,
+                         const float* const_decay, int32_t heads, int32_t dk, int32_t dv, const int32_t* seg_slot,
+                         int32_t n_seg, const int32_t* seg_sub0, const int32_t* seg_nsub, const int32_t* sub_start,
+                         const int32_t* sub_len, int32_t n_sub, float* scratch, float* piece_decay, float* state,
+                         float* out, int64_t ld_out, prl_stream_t stream);
+/* matrix-memory LSTM: stabilised exponential gates (keep, take) per head and token with the running maximum m carried
+ * in m_state[slot][head]; values with a one appended per head; output normaliser, head norm, gain and sigmoid gate */
+int prl_mlstm_gates(const float* P, int64_t ldp, int32_t off_i, int32_t off_f, const float* bias_i, const float* bias_f,
+                    float cap, int32_t H, const int32_t* seg_start, const int32_t* seg_len, const int32_t* seg_slot,
+                    int32_t n_seg, float* m_state, float* gates, float* minv, prl_stream_t stream);
+int prl_append_one(const float* P, int64_t ldp, int32_t off_v, int32_t n, int32_t H, int32_t dv, float* out,
+                   prl_stream_t stream);
+int prl_mlstm_out(const float* o_aug, int32_t n, int32_t H, int32_t dv, const float* minv, float den_eps, const float* g,
+                  int64_t ldg, const float* gain, float eps, void* out, int32_t f32, prl_stream_t stream);
+/* routed feed-forward: top-k routing + grouping of the (choice, row) pairs by expert; grouped GEMM over the tile table;
+ * gated activation with the pair's weight folded into gate and up */
+int64_t prl_moe_max_tiles(int64_t pairs, int32_t experts);
+int prl_moe_route(const float* logits, int64_t ld, int32_t n, int32_t experts, int32_t top, int32_t softmax_weights,
+                  int32_t* sel, float* wsel, int32_t* perm, int32_t* meta, int32_t* tiles, prl_stream_t stream);
+int prl_moe_gemm(const void* A, int32_t a_is_f32, int64_t lda, int32_t a_mod, const void* W, int32_t w_is_f32,
+                 int64_t expert_stride, int64_t ldw, const int32_t* perm, const int32_t* meta, const int32_t* tiles,
+                 int64_t max_tiles, int64_t N, int64_t K, float* C, int64_t ldc, int32_t c_perm, prl_stream_t stream);
+int prl_moe_glu(const float* gate_up, int64_t ld, int64_t pairs, int32_t F, const int32_t* perm, const float* wsel,
+                float limit, float beta, void* out, int32_t f32, prl_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

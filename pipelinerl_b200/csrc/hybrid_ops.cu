@@ -302,6 +302,262 @@ __global__ void decode_rows_kernel(const uint8_t* __restrict__ active, int B, in
   row_slot[b] = a ? b : -1;
 }
 
+// x = embed[token] * scale + sinusoidal position vector: channel 2i carries sin(pos * freq[i]), channel 2i+1 the cosine
+// (freq[i] = base^(-2i/W), given in double; the angle is formed and reduced in double as for the rotary embedding).
+// Written to the fp32 residual, to its operand-type copy xa and (x0a != NULL) to a second copy that later layers read
+// as "the embedding output".
+template <typename T>
+__global__ void embed_sinusoid_kernel(const int32_t* __restrict__ tokens, const T* __restrict__ embed, float scale,
+                                      const double* __restrict__ freq, const int32_t* __restrict__ row_pos, int W, int vocab,
+                                      float* __restrict__ x, T* __restrict__ xa, T* __restrict__ x0a) {
+  pdl_wait();
+  const int r = blockIdx.x;
+  int tok = tokens[r];
+  tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
+  const int pos = row_pos[r];
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    const double ang = (double)pos * freq[c >> 1];
+    const double turns = rint(ang * 0.15915494309189535);
+    const float red_ang = (float)fma(-turns, 6.283185307179586, ang);
+    float sn, cn;
+    sincosf(red_ang, &sn, &cn);
+    const float v = ldf(embed, (int64_t)tok * W + c) * scale + ((c & 1) ? cn : sn);
+    x[(int64_t)r * W + c] = v;
+    stf(xa, (int64_t)r * W + c, v);
+    if (x0a) stf(x0a, (int64_t)r * W + c, v);
+  }
+}
+
+// out[r] = [a[r] | b[r]]  (two row blocks of width W side by side: the operand of a projection that reads both)
+template <typename T>
+__global__ void concat_rows_kernel(const T* __restrict__ a, const T* __restrict__ b, int W, T* __restrict__ out) {
+  pdl_wait();
+  const int64_t r = blockIdx.x;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    out[r * 2 * W + c] = a[r * W + c];
+    out[r * 2 * W + W + c] = b[r * W + c];
+  }
+}
+
+// The close of a sublayer whose branches, sum and successor all carry their own RMS norms:
+//   b_i = y_i / rms(y_i) * gain_i   (gain_i == NULL: b_i = y_i)              i = 0, 1 (y1 may be absent)
+//   v   = s0 b_0 + s1 b_1
+//   v   = v / rms(v) * post_gain    (post_gain == NULL: unchanged)
+//   x   = (add ? x : 0) + v + bias  (bias == NULL: none)
+//   xa  = T(x / rms(x) * next_gain) (next_gain == NULL: T(x)) -- the input of the NEXT sublayer's projection
+// y_i may arrive as split-K partial slices [n_split][n][ld] of a GEMM (or as the per-choice outputs of a routed
+// feed-forward): they are summed here in slice order.  One block per row; the row stays in shared memory.
+template <typename T>
+__global__ void sublayer_close_kernel(const float* __restrict__ y0, int64_t ld0, int ns0, int64_t stride0,
+                                      const float* __restrict__ gain0, float s0, const float* __restrict__ y1, int64_t ld1,
+                                      int ns1, int64_t stride1, const float* __restrict__ gain1, float s1,
+                                      const float* __restrict__ post_gain, const float* __restrict__ bias, int add,
+                                      const float* __restrict__ next_gain, float eps, int W, float* __restrict__ x,
+                                      T* __restrict__ xa) {
+  pdl_wait();
+  extern __shared__ float rowbuf[];    // [W] y0 (then v, then x) | [W] y1
+  __shared__ float red[32];
+  float* b0 = rowbuf;
+  float* b1 = rowbuf + W;
+  const int64_t r = blockIdx.x;
+  float ss0 = 0.f, ss1 = 0.f;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    float a = 0.f;
+    for (int k = 0; k < ns0; ++k) a += y0[k * stride0 + r * ld0 + c];
+    b0[c] = a;
+    ss0 += a * a;
+    if (y1) {
+      float b = 0.f;
+      for (int k = 0; k < ns1; ++k) b += y1[k * stride1 + r * ld1 + c];
+      b1[c] = b;
+      ss1 += b * b;
+    }
+  }
+  float i0 = 1.f, i1 = 1.f;
+  if (gain0) i0 = 1.f / sqrtf(block_sum(ss0, red) / (float)W + eps);
+  if (y1 && gain1) i1 = 1.f / sqrtf(block_sum(ss1, red) / (float)W + eps);
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {        // every thread touches only the columns it wrote
+    float v = s0 * (gain0 ? b0[c] * i0 * gain0[c] : b0[c]);
+    if (y1) v += s1 * (gain1 ? b1[c] * i1 * gain1[c] : b1[c]);
+    b0[c] = v;
+    ss += v * v;
+  }
+  float ip = 1.f;
+  if (post_gain) ip = 1.f / sqrtf(block_sum(ss, red) / (float)W + eps);
+  float sx = 0.f;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    float v = post_gain ? b0[c] * ip * post_gain[c] : b0[c];
+    if (bias) v += bias[c];
+    if (add) v += x[r * W + c];
+    x[r * W + c] = v;
+    b0[c] = v;
+    sx += v * v;
+  }
+  float in = 1.f;
+  if (next_gain) in = 1.f / sqrtf(block_sum(sx, red) / (float)W + eps);
+  for (int c = threadIdx.x; c < W; c += blockDim.x) stf(xa, r * W + c, next_gain ? b0[c] * in * next_gain[c] : b0[c]);
+}
+
+// Attention front end with PER-HEAD unit norms: q and k get their biases (NULL: none), every head of q and of k is
+// divided by its own root mean square over `dim` and multiplied by a gain (NULL: none; indexed head * dim + channel);
+// q goes to the query buffer, k into the paged cache.  The value written beside it is either the key as projected
+// (bias added, BEFORE its norm: off_v < 0, then vdim == dim) or columns off_v.. of P (bias-free).  One warp per head.
+template <typename T>
+__global__ void qk_headnorm_cache_kernel(const float* __restrict__ P, int64_t ldp, int off_q, int off_k, int off_v, int H,
+                                         int G, int dim, int vdim, const float* __restrict__ q_bias,
+                                         const float* __restrict__ k_bias, const float* __restrict__ q_gain,
+                                         const float* __restrict__ k_gain, float eps, const int32_t* __restrict__ row_pos,
+                                         const int32_t* __restrict__ row_slot, const int32_t* __restrict__ block_table,
+                                         int max_blocks, int page_size, T* __restrict__ q_out, T* __restrict__ k_pool,
+                                         T* __restrict__ v_pool) {
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int slot = row_slot[r];
+  if (slot < 0) return;
+  const int pos = row_pos[r];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int page = block_table[(int64_t)slot * max_blocks + pos / page_size], within = pos % page_size;
+  for (int hh = warp; hh < H + G; hh += nw) {
+    const bool is_q = hh < H;
+    const int head = is_q ? hh : hh - H;
+    const float* src = P + (int64_t)r * ldp + (is_q ? off_q : off_k) + head * dim;
+    const float* bias = is_q ? q_bias : k_bias;
+    const float* gain = is_q ? q_gain : k_gain;
+    float ss = 0.f;
+    for (int j = lane; j < dim; j += 32) {
+      const float v = src[j] + (bias ? bias[head * dim + j] : 0.f);
+      ss += v * v;
+    }
+    ss = warp_sum(ss);
+    const float inv = 1.f / sqrtf(ss / (float)dim + eps);
+    for (int j = lane; j < dim; j += 32) {
+      const float raw = src[j] + (bias ? bias[head * dim + j] : 0.f);
+      const float v = raw * inv * (gain ? gain[head * dim + j] : 1.f);
+      if (is_q) {
+        stf(q_out, ((int64_t)r * H + head) * dim + j, v);
+      } else {
+        const int64_t at = (((int64_t)page * G + head) * page_size + within) * dim + j;
+        stf(k_pool, at, v);
+        if (off_v < 0) stf(v_pool, at, raw);
+      }
+    }
+  }
+  if (off_v >= 0) {
+    const float* v = P + (int64_t)r * ldp + off_v;
+    for (int i = threadIdx.x; i < G * vdim; i += blockDim.x) {
+      const int head = i / vdim, j = i % vdim;
+      stf(v_pool, (((int64_t)page * G + head) * page_size + within) * vdim + j, v[i]);
+    }
+  }
+}
+
+// In-place activation of a column range of the projection buffer: 0 = SiLU
+__global__ void act_cols_kernel(float* __restrict__ P, int64_t ld, int off, int C, int act) {
+  pdl_wait();
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float* p = P + (int64_t)blockIdx.x * ld + off + c;
+  *p = silu_f(*p);
+}
+
+// Feed-forward activations of one input: 0 = relu(z)^2
+template <typename T>
+__global__ void act_store_kernel(const float* __restrict__ P, int64_t ld, int F, int act, T* __restrict__ out) {
+  pdl_wait();
+  const int64_t r = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= F) return;
+  const float z = fmaxf(P[r * ld + c], 0.f);
+  stf(out, r * F + c, z * z);
+}
+
+// ---- matrix-memory LSTM (mLSTM) --------------------------------------------------------------------------------------
+// Gates of the stabilised recurrence, per head:  i = cap tanh((zi + bi) / cap),  f = logsigmoid(cap tanh((zf + bf) / cap)),
+//   m_t = max(f + m_(t-1), i),   keep_t = exp(f + m_(t-1) - m_t),   take_t = exp(i - m_t)
+// so that S_t = keep_t S_(t-1) + take_t k v^T is what prl_decay_scan runs.  m is carried per sequence slot (0 at the
+// start); the walk over a segment's tokens is sequential, one warp per head: 32 tokens' transcendentals at a time in
+// parallel, the max-chain through shuffles.  gates[row][head] = (keep, take); minv[row][head] = exp(-m_t).
+__device__ __forceinline__ float logsigmoid_g(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
+
+__global__ void mlstm_gates_kernel(const float* __restrict__ P, int64_t ldp, int off_i, int off_f,
+                                   const float* __restrict__ bias_i, const float* __restrict__ bias_f, float cap, int H,
+                                   const int32_t* __restrict__ seg_start, const int32_t* __restrict__ seg_len,
+                                   const int32_t* __restrict__ seg_slot, float* __restrict__ m_state,
+                                   float* __restrict__ gates, float* __restrict__ minv) {
+  pdl_wait();
+  const int seg = blockIdx.x;
+  const int len = seg_len[seg];
+  if (len <= 0) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int64_t row0 = seg_start[seg];
+  const int slot = seg_slot[seg];
+  for (int h = warp; h < H; h += nw) {
+    float m = m_state[(int64_t)slot * H + h];
+    for (int t0 = 0; t0 < len; t0 += 32) {
+      const int t = t0 + lane;
+      float gi = 0.f, gf = 0.f;
+      if (t < len) {
+        const float* pr = P + (row0 + t) * ldp;
+        gi = cap * tanhf((pr[off_i + h] + bias_i[h]) / cap);
+        gf = logsigmoid_g(cap * tanhf((pr[off_f + h] + bias_f[h]) / cap));
+      }
+      float m_prev = 0.f, m_mine = 0.f;
+      const int nt = min(32, len - t0);
+      for (int j = 0; j < nt; ++j) {
+        const float fj = __shfl_sync(0xffffffffu, gf, j), ij = __shfl_sync(0xffffffffu, gi, j);
+        const float m_new = fmaxf(fj + m, ij);
+        if (j == lane) { m_prev = m; m_mine = m_new; }
+        m = m_new;
+      }
+      if (t < len) {
+        const int64_t o = (row0 + t) * H + h;
+        gates[2 * o] = expf(gf + m_prev - m_mine);
+        gates[2 * o + 1] = expf(gi - m_mine);
+        minv[o] = expf(-m_mine);
+      }
+    }
+    if (lane == 0) m_state[(int64_t)slot * H + h] = m;
+  }
+}
+
+// Values of the scan with a ONE appended per head: [row][head][dv + 1], so that the recurrence also carries the
+// normaliser n_t = keep n + take k as the last value column and returns n_t . q beside S_t^T q.
+__global__ void append_one_kernel(const float* __restrict__ P, int64_t ldp, int off_v, int H, int dv, float* __restrict__ out) {
+  pdl_wait();
+  const int64_t r = blockIdx.x;
+  const int C = H * (dv + 1);
+  for (int i = threadIdx.x; i < C; i += blockDim.x) {
+    const int h = i / (dv + 1), c = i - h * (dv + 1);
+    out[r * C + i] = c < dv ? P[r * ldp + off_v + h * dv + c] : 1.f;
+  }
+}
+
+// o = (S^T q) / (max(|n . q|, exp(-m)) + den_eps) per head, divided by its root mean square over the head, times a gain
+// over all heads' channels, times sigmoid(g); written in the operand type of the output projection.  Block per (row, head).
+template <typename T>
+__global__ void mlstm_out_kernel(const float* __restrict__ o_aug, int H, int dv, const float* __restrict__ minv,
+                                 float den_eps, const float* __restrict__ g, int64_t ldg, const float* __restrict__ gain,
+                                 float eps, T* __restrict__ out) {
+  pdl_wait();
+  __shared__ float red[32];
+  const int64_t r = blockIdx.x;
+  const int h = blockIdx.y;
+  const float* o = o_aug + (r * H + h) * (dv + 1);
+  const float den = fmaxf(fabsf(o[dv]), minv[r * H + h]) + den_eps;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < dv; c += blockDim.x) {
+    const float v = o[c] / den;
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.f / sqrtf(ss / (float)dv + eps);
+  for (int c = threadIdx.x; c < dv; c += blockDim.x) {
+    const int ch = h * dv + c;
+    stf(out, r * H * dv + ch, o[c] / den * inv * gain[ch] * sigmoid_f(g[r * ldg + ch]));
+  }
+}
+
 inline int row_threads(int width) {
   int t = ((width + 31) / 32) * 32;
   return t < 32 ? 32 : (t > 256 ? 256 : t);
@@ -426,6 +682,117 @@ extern "C" int prl_conv_state_update(const float* P, int64_t ldp, int32_t off, i
 extern "C" int prl_decode_rows(const uint8_t* active, int32_t B, int32_t* seg_len, int32_t* row_slot, prl_stream_t st) {
   PRL_CHECK_ARG(active && seg_len && row_slot && B >= 1, "prl_decode_rows: bad argument");
   PRL_CUDA(launch_pdl(decode_rows_kernel, dim3((B + 127) / 128), dim3(128), (size_t)(0), (cudaStream_t)st, active, B, seg_len, row_slot));
+  PRL_LAUNCH_CHECK();
+  return PRL_OK;
+}
+
+extern "C" int prl_embed_sinusoid(const int32_t* tokens, const void* embed, int32_t f32, float scale, const double* freq,
+                                  const int32_t* row_pos, int32_t n, int32_t W, int32_t vocab, float* x, void* xa, void* x0a,
+                                  prl_stream_t st) {
+  PRL_CHECK_ARG(tokens && embed && freq && row_pos && x && xa && n >= 1 && W >= 1 && vocab >= 1, "prl_embed_sinusoid: bad argument");
+  if (f32) PRL_CUDA(launch_pdl(embed_sinusoid_kernel<float>, dim3(n), dim3(row_threads(W)), (size_t)(0), (cudaStream_t)st, tokens, (const float*)embed, scale, freq, row_pos, W, vocab, x, (float*)xa, (float*)x0a));
+  else PRL_CUDA(launch_pdl(embed_sinusoid_kernel<bf16>, dim3(n), dim3(row_threads(W)), (size_t)(0), (cudaStream_t)st, tokens, (const bf16*)embed, scale, freq, row_pos, W, vocab, x, (bf16*)xa, (bf16*)x0a));
+  PRL_LAUNCH_CHECK();
+  return PRL_OK;
+}
+
+extern "C" int prl_concat_rows(const void* a, const void* b, int32_t n, int32_t W, void* out, int32_t f32, prl_stream_t st) {
+  PRL_CHECK_ARG(a && b && out && n >= 1 && W >= 1, "prl_concat_rows: bad argument");
+  if (f32) PRL_CUDA(launch_pdl(concat_rows_kernel<float>, dim3(n), dim3(row_threads(W)), (size_t)(0), (cudaStream_t)st, (const float*)a, (const float*)b, W, (float*)out));
+  else PRL_CUDA(launch_pdl(concat_rows_kernel<bf16>, dim3(n), dim3(row_threads(W)), (size_t)(0), (cudaStream_t)st, (const bf16*)a, (const bf16*)b, W, (bf16*)out));
+  PRL_LAUNCH_CHECK();
+  return PRL_OK;
+}
+
+extern "C" int prl_sublayer_close(const float* y0, int64_t ld0, int32_t n_split0, const float* gain0, float s0,
+                                  const float* y1, int64_t ld1, int32_t n_split1, const float* gain1, float s1,
+                                  const float* post_gain, const float* bias, int32_t add, const float* next_gain, float eps,
+                                  int32_t n, int32_t W, float* x, void* xa, int32_t f32, prl_stream_t st) {
+  PRL_CHECK_ARG(y0 && x && xa && n >= 1 && W >= 1 && ld0 >= W && (!y1 || ld1 >= W) && n_split0 >= 1 && (!y1 || n_split1 >= 1),
+                "prl_sublayer_close: bad argument");
+  const size_t smem = 2 * (size_t)W * sizeof(float);
+  PRL_CHECK_ARG(smem <= 200 * 1024, "prl_sublayer_close: a row of %d channels does not fit in shared memory", W);
+  const int64_t st0 = (int64_t)n * ld0, st1 = (int64_t)n * ld1;
+  int th = ((W + 31) / 32) * 32;
+  const int cap = n <= 256 ? 1024 : 256;     // few rows: more threads per row; many rows: more rows per SM
+  th = th > cap ? cap : th;
+  static SmemAttr attr_f = {}, attr_b = {};
+  if (f32) {
+    if (smem > 48 * 1024) PRL_CUDA(ensure_smem(sublayer_close_kernel<float>, (int)smem, attr_f));
+    PRL_CUDA(launch_pdl(sublayer_close_kernel<float>, dim3(n), dim3(th), smem, (cudaStream_t)st, y0, ld0, n_split0, st0, gain0, s0, y1, ld1, n_split1, st1, gain1, s1, post_gain, bias, add, next_gain, eps, W, x, (float*)xa));
+  } else {
+    if (smem > 48 * 1024) PRL_CUDA(ensure_smem(sublayer_close_kernel<bf16>, (int)smem, attr_b));
+    PRL_CUDA(launch_pdl(sublayer_close_kernel<bf16>, dim3(n), dim3(th), smem, (cudaStream_t)st, y0, ld0, n_split0, st0, gain0, s0, y1, ld1, n_split1, st1, gain1, s1, post_gain, bias, add, next_gain, eps, W, x, (bf16*)xa));
+  }
+  PRL_LAUNCH_CHECK();
+  return PRL_OK;
+}
+
+extern "C" int prl_qk_headnorm_cache(const float* P, int64_t ldp, int32_t off_q, int32_t off_k, int32_t off_v, int32_t n,
+                                     int32_t H, int32_t G, int32_t dim, int32_t vdim, const float* q_bias,
+                                     const float* k_bias, const float* q_gain, const float* k_gain, float eps,
+                                     const int32_t* row_pos, const int32_t* row_slot, const int32_t* block_table,
+                                     int32_t max_blocks, int32_t page_size, void* q_out, void* k_pool, void* v_pool,
+                                     int32_t f32, prl_stream_t st) {
+  PRL_CHECK_ARG(P && row_pos && row_slot && block_table && q_out && k_pool && v_pool, "prl_qk_headnorm_cache: NULL argument");
+  PRL_CHECK_ARG(n >= 1 && H >= 1 && G >= 1 && dim >= 1 && vdim >= 1 && (off_v >= 0 || vdim == dim) && page_size >= 1 &&
+                max_blocks >= 1, "prl_qk_headnorm_cache: bad shape (H=%d G=%d dim=%d vdim=%d)", H, G, dim, vdim);
+  int th = 32 * (H + G);
+  th = th > 256 ? 256 : th;
+  cudaStream_t s = (cudaStream_t)st;
+  if (f32) PRL_CUDA(launch_pdl(qk_headnorm_cache_kernel<float>, dim3(n), dim3(th), (size_t)0, s, P, ldp, off_q, off_k, off_v, H, G, dim, vdim, q_bias, k_bias, q_gain, k_gain, eps,
+        row_pos, row_slot, block_table, max_blocks, page_size, (float*)q_out, (float*)k_pool, (float*)v_pool));
+  else PRL_CUDA(launch_pdl(qk_headnorm_cache_kernel<bf16>, dim3(n), dim3(th), (size_t)0, s, P, ldp, off_q, off_k, off_v, H, G, dim, vdim, q_bias, k_bias, q_gain, k_gain, eps,
+        row_pos, row_slot, block_table, max_blocks, page_size, (bf16*)q_out, (bf16*)k_pool, (bf16*)v_pool));
+  PRL_LAUNCH_CHECK();
+  return PRL_OK;
+}
+
+extern "C" int prl_act_cols(float* P, int64_t ld, int32_t off, int32_t n, int32_t C, int32_t act, prl_stream_t st) {
+  PRL_CHECK_ARG(P && n >= 1 && C >= 1 && off >= 0 && ld >= off + C && act == 0, "prl_act_cols: bad argument");
+  PRL_CUDA(launch_pdl(act_cols_kernel, dim3(n, (C + 255) / 256), dim3(256), (size_t)0, (cudaStream_t)st, P, ld, off, C, act));
+  PRL_LAUNCH_CHECK();
+  return PRL_OK;
+}
+
+extern "C" int prl_act_store(const float* P, int64_t ld, int32_t n, int32_t F, int32_t act, void* out, int32_t f32, prl_stream_t st) {
+  PRL_CHECK_ARG(P && out && n >= 1 && F >= 1 && ld >= F && act == 0, "prl_act_store: bad argument");
+  dim3 grid(n, (F + 255) / 256);
+  if (f32) PRL_CUDA(launch_pdl(act_store_kernel<float>, grid, dim3(256), (size_t)0, (cudaStream_t)st, P, ld, F, act, (float*)out));
+  else PRL_CUDA(launch_pdl(act_store_kernel<bf16>, grid, dim3(256), (size_t)0, (cudaStream_t)st, P, ld, F, act, (bf16*)out));
+  PRL_LAUNCH_CHECK();
+  return PRL_OK;
+}
+
+extern "C" int prl_mlstm_gates(const float* P, int64_t ldp, int32_t off_i, int32_t off_f, const float* bias_i,
+                               const float* bias_f, float cap, int32_t H, const int32_t* seg_start, const int32_t* seg_len,
+                               const int32_t* seg_slot, int32_t n_seg, float* m_state, float* gates, float* minv,
+                               prl_stream_t st) {
+  PRL_CHECK_ARG(P && bias_i && bias_f && seg_start && seg_len && seg_slot && m_state && gates && minv && H >= 1 && n_seg >= 1 &&
+                cap > 0.f, "prl_mlstm_gates: bad argument");
+  int th = 32 * H;
+  th = th > 256 ? 256 : th;
+  PRL_CUDA(launch_pdl(mlstm_gates_kernel, dim3(n_seg), dim3(th), (size_t)0, (cudaStream_t)st, P, ldp, off_i, off_f, bias_i, bias_f, cap, H, seg_start, seg_len, seg_slot, m_state, gates, minv));
+  PRL_LAUNCH_CHECK();
+  return PRL_OK;
+}
+
+extern "C" int prl_append_one(const float* P, int64_t ldp, int32_t off_v, int32_t n, int32_t H, int32_t dv, float* out,
+                              prl_stream_t st) {
+  PRL_CHECK_ARG(P && out && n >= 1 && H >= 1 && dv >= 1, "prl_append_one: bad argument");
+  PRL_CUDA(launch_pdl(append_one_kernel, dim3(n), dim3(row_threads(H * (dv + 1))), (size_t)0, (cudaStream_t)st, P, ldp, off_v, H, dv, out));
+  PRL_LAUNCH_CHECK();
+  return PRL_OK;
+}
+
+extern "C" int prl_mlstm_out(const float* o_aug, int32_t n, int32_t H, int32_t dv, const float* minv, float den_eps,
+                             const float* g, int64_t ldg, const float* gain, float eps, void* out, int32_t f32,
+                             prl_stream_t st) {
+  PRL_CHECK_ARG(o_aug && minv && g && gain && out && n >= 1 && H >= 1 && H <= 65535 && dv >= 1, "prl_mlstm_out: bad argument");
+  dim3 grid(n, H);
+  const int th = row_threads(dv);
+  if (f32) PRL_CUDA(launch_pdl(mlstm_out_kernel<float>, grid, dim3(th), (size_t)0, (cudaStream_t)st, o_aug, H, dv, minv, den_eps, g, ldg, gain, eps, (float*)out));
+  else PRL_CUDA(launch_pdl(mlstm_out_kernel<bf16>, grid, dim3(th), (size_t)0, (cudaStream_t)st, o_aug, H, dv, minv, den_eps, g, ldg, gain, eps, (bf16*)out));
   PRL_LAUNCH_CHECK();
   return PRL_OK;
 }

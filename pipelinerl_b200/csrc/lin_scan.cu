@@ -9,6 +9,10 @@
 //          and the output is scaled by q_scale;
 //   SSD    state-space duality (Mamba-2): v = x (convolved), k = dt * B, q = C, the decay is one scalar per head,
 //          a = exp(-exp(A_log) * dt) with dt = softplus(dt_raw + dt_bias), and skip = D.
+//   SCALAR one decay and one input scale per head and token, S_t = a_t S_(t-1) + b_t k_t v_t^T: either a constant decay per
+//          head with b = 1 (lightning attention) or (a_t, b_t) pairs formed beforehand (the stabilised exponential gates
+//          of a matrix-memory LSTM, prl_mlstm_gates); q, k, v are columns of the projection buffer, the output is scaled
+//          by q_scale.
 // Everything that enters the recurrence is fp32.
 //
 // Work split: grid (value tiles, heads, segments), 64 threads per CTA.  Thread t owns VC adjacent value columns
@@ -48,6 +52,8 @@ struct ScanArgs {
   const float* dt_raw; int64_t ld_dt; int off_dt; int groups;
   const float* dt_bias; const float* a_log; const float* skip;
   int vec4;   // every staged vector starts on a 16-byte boundary and dk, dv are multiples of 4: 16-byte cp.async
+  // SCALAR: (decay, input scale) pairs at dt_raw[row * ld_dt + off_dt + 2 * head], or, if dt_raw is null, the constant
+  // decay a_log[head] with input scale 1
   int zero_init;   // the state starts at zero instead of being read (seg_slot may then be null: slot = segment index)
 };
 
@@ -66,14 +72,17 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-template <int R, int VC, bool SSD>
+constexpr int kGated = 0, kSsd = 1, kScalar = 2;
+
+template <int R, int VC, int MODE>
 __global__ void __launch_bounds__(kThreads) lin_scan_kernel(ScanArgs a) {
+  constexpr bool SSD = MODE == kSsd, SCL = MODE == kScalar, ONE = SSD || SCL;   // ONE: one decay per head and token
   pdl_wait();   // launched with the programmatic-serialization attribute like the engine's other step kernels; no early
                 // trigger: letting the next grid become resident early measured +3 ms on a 4096-token prefill and +-0 on decode
   constexpr int kCols = kKeyLanes * VC;          // value columns per CTA
   constexpr int RS = R + 4;                      // padded stride of one thread's key-channel block (conflict-free LDS.128)
   constexpr int kVecTok = kKeyLanes * RS;        // floats per token and vector
-  constexpr int kNVec = SSD ? 2 : 3;
+  constexpr int kNVec = ONE ? 2 : 3;
   constexpr int kBuf = kChunk * (kNVec * kVecTok + kCols + 2);
   extern __shared__ __align__(16) float sm[];
   const int seg = blockIdx.z, h = blockIdx.y, vt = blockIdx.x;
@@ -105,12 +114,13 @@ __global__ void __launch_bounds__(kThreads) lin_scan_kernel(ScanArgs a) {
   const int grp = SSD ? h / (a.heads / a.groups) : 0;
   float skip = 0.f, neg_a = 0.f, dtb = 0.f;
   if (SSD) { skip = a.skip[h]; neg_a = -expf(a.a_log[h]); dtb = a.dt_bias[h]; }
+  const float cdec = (SCL && !a.dt_raw) ? a.a_log[h] : 0.f;
   for (int i = tid; i < 2 * kBuf; i += kThreads) sm[i] = 0.f;   // padding slots (d >= dk, v >= dv) stay zero for good
   __syncthreads();
 
   const float* kbase = a.kvec + a.off_k + (SSD ? grp : h) * dk;
   const float* qbase = a.qvec + a.off_q + (SSD ? grp : h) * dk;
-  const float* abase = SSD ? nullptr : a.avec + h * dk;
+  const float* abase = ONE ? nullptr : a.avec + h * dk;
   const float* xbase = a.xval + a.off_x + h * dv + vt * kCols;
   const int cols_here = min(kCols, dv - vt * kCols);
 
@@ -128,7 +138,7 @@ __global__ void __launch_bounds__(kThreads) lin_scan_kernel(ScanArgs a) {
           const int o = t * kVecTok + (d / R) * RS + (d % R);
           cp_async16(bk + o, kbase + r * a.ld_k + d);
           cp_async16(bq + o, qbase + r * a.ld_q + d);
-          if (!SSD) cp_async16(ba + o, abase + r * a.ld_a + d);
+          if (!ONE) cp_async16(ba + o, abase + r * a.ld_a + d);
         }
       }
       for (int i = tid * 4; i < nt * kCols; i += kThreads * 4) {
@@ -142,7 +152,7 @@ __global__ void __launch_bounds__(kThreads) lin_scan_kernel(ScanArgs a) {
           const int o = t * kVecTok + (d / R) * RS + (d % R);
           cp_async4(bk + o, kbase + r * a.ld_k + d);
           cp_async4(bq + o, qbase + r * a.ld_q + d);
-          if (!SSD) cp_async4(ba + o, abase + r * a.ld_a + d);
+          if (!ONE) cp_async4(ba + o, abase + r * a.ld_a + d);
         }
       }
       for (int i = tid; i < nt * kCols; i += kThreads) {
@@ -151,6 +161,11 @@ __global__ void __launch_bounds__(kThreads) lin_scan_kernel(ScanArgs a) {
       }
     }
     if (SSD && tid < nt) cp_async4(bs + tid, a.dt_raw + (row0 + t0 + tid) * a.ld_dt + a.off_dt + h);
+    if (SCL && a.dt_raw && tid < nt) {
+      const float* gp = a.dt_raw + (row0 + t0 + tid) * a.ld_dt + a.off_dt + 2 * h;
+      cp_async4(bs + kChunk + tid, gp);      // decay
+      cp_async4(bs + tid, gp + 1);           // input scale
+    }
     cp_async_commit();
   };
 
@@ -179,15 +194,19 @@ __global__ void __launch_bounds__(kThreads) lin_scan_kernel(ScanArgs a) {
       }
       __syncthreads();
     }
+    if (SCL && !a.dt_raw) {
+      if (tid < nt) { bs[tid] = 1.f; bs[kChunk + tid] = cdec; }
+      __syncthreads();
+    }
     auto token = [&](int t) {
       float xv[VC], xin[VC], acc[VC];
 #pragma unroll
       for (int j = 0; j < VC; ++j) {
         xv[j] = bx[t * kCols + vg * VC + j];
-        xin[j] = SSD ? xv[j] * bs[t] : xv[j];
+        xin[j] = ONE ? xv[j] * bs[t] : xv[j];
         acc[j] = 0.f;
       }
-      const float dec = SSD ? bs[kChunk + t] : 0.f;
+      const float dec = ONE ? bs[kChunk + t] : 0.f;
       const float* pk = bk + t * kVecTok + dg * RS;
       const float* pq = bq + t * kVecTok + dg * RS;
       const float* pa = ba + t * kVecTok + dg * RS;
@@ -197,7 +216,7 @@ __global__ void __launch_bounds__(kThreads) lin_scan_kernel(ScanArgs a) {
           const float4 k4 = *reinterpret_cast<const float4*>(pk + 4 * i4);
           const float4 q4 = *reinterpret_cast<const float4*>(pq + 4 * i4);
           float4 a4 = make_float4(dec, dec, dec, dec);
-          if (!SSD) a4 = *reinterpret_cast<const float4*>(pa + 4 * i4);
+          if (!ONE) a4 = *reinterpret_cast<const float4*>(pa + 4 * i4);
           const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w}, aa[4] = {a4.x, a4.y, a4.z, a4.w};
 #pragma unroll
           for (int u = 0; u < 4; ++u)
@@ -210,7 +229,7 @@ __global__ void __launch_bounds__(kThreads) lin_scan_kernel(ScanArgs a) {
       } else {
 #pragma unroll
         for (int i = 0; i < R; ++i) {
-          const float kk = pk[i], qq = pq[i], aa = SSD ? dec : pa[i];
+          const float kk = pk[i], qq = pq[i], aa = ONE ? dec : pa[i];
 #pragma unroll
           for (int j = 0; j < VC; ++j) {
             s[i][j] = fmaf(aa, s[i][j], kk * xin[j]);
@@ -263,10 +282,10 @@ int plan_r(int dk) {
   return r;
 }
 
-template <int R, int VC, bool SSD>
+template <int R, int VC, int SSD>
 int launch_one(const ScanArgs& a, int n_seg, cudaStream_t st) {
   constexpr int kCols = kKeyLanes * VC;
-  constexpr int kNVec = SSD ? 2 : 3;
+  constexpr int kNVec = SSD != kGated ? 2 : 3;
   const size_t smem = 2 * (size_t)kChunk * (kNVec * kKeyLanes * (R + 4) + kCols + 2) * sizeof(float);
   static SmemAttr attr = {};
   if (smem > 48 * 1024) PRL_CUDA(ensure_smem(lin_scan_kernel<R, VC, SSD>, (int)smem, attr));
@@ -277,7 +296,7 @@ int launch_one(const ScanArgs& a, int n_seg, cudaStream_t st) {
 }
 
 // value columns per thread: the widest tile that still gives two CTAs per SM
-template <int R, bool SSD>
+template <int R, int SSD>
 int launch_r(const ScanArgs& a, int n_seg, cudaStream_t st) {
   const int64_t want = 2 * (int64_t)num_sms();
   auto ctas = [&](int vc) { return (int64_t)((a.dv + 8 * vc - 1) / (8 * vc)) * a.heads * n_seg; };
@@ -288,11 +307,11 @@ int launch_r(const ScanArgs& a, int n_seg, cudaStream_t st) {
 
 inline bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 
-template <bool SSD>
+template <int SSD>
 int launch_scan(ScanArgs a, int n_seg, cudaStream_t st) {
   a.vec4 = (a.dk % 4 == 0 && a.dv % 4 == 0 && a.ld_k % 4 == 0 && a.ld_q % 4 == 0 && a.ld_x % 4 == 0 && a.off_k % 4 == 0 &&
             a.off_q % 4 == 0 && a.off_x % 4 == 0 && aligned16(a.kvec) && aligned16(a.qvec) && aligned16(a.xval) &&
-            (SSD || (a.ld_a % 4 == 0 && aligned16(a.avec)))) ? 1 : 0;
+            (SSD != kGated || (a.ld_a % 4 == 0 && aligned16(a.avec)))) ? 1 : 0;
   switch (plan_r(a.dk)) {
     case 1: return launch_r<1, SSD>(a, n_seg, st);
     case 2: return launch_r<2, SSD>(a, n_seg, st);
@@ -337,8 +356,9 @@ struct SplitArgs {
   int r;                                                 // key channels per key lane in the state layout
 };
 
-template <bool SSD>
+template <int MODE>
 __global__ void __launch_bounds__(256) piece_decay_kernel(ScanArgs a, SplitArgs p) {
+  constexpr bool SSD = MODE == kSsd, SCL = MODE == kScalar;
   pdl_wait();
   const int sub = blockIdx.x, h = blockIdx.y, d = threadIdx.x, dpad = kKeyLanes * p.r;
   if (d >= dpad) return;
@@ -346,13 +366,15 @@ __global__ void __launch_bounds__(256) piece_decay_kernel(ScanArgs a, SplitArgs 
   const int64_t row0 = p.sub_start[sub];
   float prod = 1.f;                    // eight loads in flight at a time; the product keeps the order of the tokens
   const float neg_a = SSD ? -expf(a.a_log[h]) : 0.f, dtb = SSD ? a.dt_bias[h] : 0.f;
-  if (SSD || d < a.dk) {
+  const float cdec = (SCL && !a.dt_raw) ? a.a_log[h] : 1.f;
+  if (SSD || SCL || d < a.dk) {
     for (int t0 = 0; t0 < len; t0 += 8) {
       float v[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const int t = min(t0 + j, len - 1);
-        v[j] = SSD ? a.dt_raw[(row0 + t) * a.ld_dt + a.off_dt + h] : a.avec[(row0 + t) * a.ld_a + h * a.dk + d];
+        if (SCL) v[j] = a.dt_raw ? a.dt_raw[(row0 + t) * a.ld_dt + a.off_dt + 2 * h] : cdec;
+        else v[j] = SSD ? a.dt_raw[(row0 + t) * a.ld_dt + a.off_dt + h] : a.avec[(row0 + t) * a.ld_a + h * a.dk + d];
       }
 #pragma unroll
       for (int j = 0; j < 8; ++j)
@@ -394,8 +416,9 @@ __global__ void __launch_bounds__(256) carry_kernel(ScanArgs a, SplitArgs p) {
   *real = s;
 }
 
-template <bool SSD>
+template <int MODE>
 __global__ void __launch_bounds__(256) apply_kernel(ScanArgs a, SplitArgs p) {
+  constexpr bool SSD = MODE == kSsd, SCL = MODE == kScalar, ONE = SSD || SCL;
   pdl_wait();
   __shared__ __align__(16) float wT[kApplyKeys * kWStride];     // [key channel][token]: q_t[d] * (decay from the piece's start through t)
   __shared__ __align__(16) float S[kApplyKeys * kApplyCols];    // [key channel][column]: the state before this piece
@@ -409,9 +432,11 @@ __global__ void __launch_bounds__(256) apply_kernel(ScanArgs a, SplitArgs p) {
   const float* sc = p.scratch + (int64_t)sub * a.state_slot_stride + (int64_t)h * r * nv4 * 32;
   const int tx = tid % 16, ty = tid / 16;      // columns 4 tx .., tokens 4 ty ..
   float acc[4][4] = {};
-  if (SSD) {
-    if (tid < kPiece)
-      dec[tid] = tid < len ? expf(-expf(a.a_log[h]) * softplus_f(a.dt_raw[(row0 + tid) * a.ld_dt + a.off_dt + h] + a.dt_bias[h])) : 1.f;
+  if (ONE) {
+    if (tid < kPiece) {
+      if (SSD) dec[tid] = tid < len ? expf(-expf(a.a_log[h]) * softplus_f(a.dt_raw[(row0 + tid) * a.ld_dt + a.off_dt + h] + a.dt_bias[h])) : 1.f;
+      else dec[tid] = tid < len ? (a.dt_raw ? a.dt_raw[(row0 + tid) * a.ld_dt + a.off_dt + 2 * h] : a.a_log[h]) : 1.f;
+    }
     __syncthreads();
     if (tid == 0) {
       float cum = 1.f;
@@ -424,7 +449,7 @@ __global__ void __launch_bounds__(256) apply_kernel(ScanArgs a, SplitArgs p) {
   // wait for each load in turn) -- then the state rows of these channels, then the product.
   for (int d0 = 0; d0 < dk; d0 += kApplyKeys) {
     const int nd = min(kApplyKeys, dk - d0);
-    if (!SSD) {
+    if (!ONE) {
       for (int e = tid; e < kPiece * nd; e += 256) {
         const int t = e / nd, d = e - t * nd;
         wT[d * kWStride + t] = t < len ? a.avec[(row0 + t) * a.ld_a + h * dk + d0 + d] : 1.f;
@@ -439,7 +464,7 @@ __global__ void __launch_bounds__(256) apply_kernel(ScanArgs a, SplitArgs p) {
     }
     for (int e = tid; e < kPiece * nd; e += 256) {
       const int t = e / nd, d = e - t * nd;
-      const float cum = SSD ? dec[t] : wT[d * kWStride + t];
+      const float cum = ONE ? dec[t] : wT[d * kWStride + t];
       wT[d * kWStride + t] = t < len ? cum * qbase[(row0 + t) * a.ld_q + d0 + d] * a.q_scale : 0.f;
     }
     for (int e = tid; e < r * (kApplyCols / 4) * kKeyLanes; e += 256) {      // key lanes fastest: whole 128-byte lines
@@ -476,7 +501,7 @@ __global__ void __launch_bounds__(256) apply_kernel(ScanArgs a, SplitArgs p) {
   }
 }
 
-template <bool SSD>
+template <int SSD>
 int launch_split(ScanArgs a, int n_seg, SplitArgs p, int n_sub, cudaStream_t st) {
   p.r = plan_r(a.dk);
   ScanArgs pieces = a;                 // 1. every piece from a zero state into its scratch slot
@@ -528,8 +553,8 @@ static int gla_scan_impl(const float* P, int64_t ldp, int32_t off_q, int32_t off
   a.avec = decay; a.ld_a = ld_decay;
   a.xval = P; a.ld_x = ldp; a.off_x = off_v;
   a.q_scale = q_scale;
-  if (split) return launch_split<false>(a, n_seg, *split, n_sub, (cudaStream_t)st);
-  return launch_scan<false>(a, n_seg, (cudaStream_t)st);
+  if (split) return launch_split<kGated>(a, n_seg, *split, n_sub, (cudaStream_t)st);
+  return launch_scan<kGated>(a, n_seg, (cudaStream_t)st);
 }
 
 extern "C" int prl_gla_scan(const float* P, int64_t ldp, int32_t off_q, int32_t off_k, int32_t off_v, float q_scale,
@@ -593,8 +618,8 @@ static int ssd_scan_impl(const float* P, int64_t ldp, int32_t off_dt, const floa
   a.q_scale = 1.f;
   a.dt_raw = P; a.ld_dt = ldp; a.off_dt = off_dt; a.groups = groups;
   a.dt_bias = dt_bias; a.a_log = a_log; a.skip = skip;
-  if (split) return launch_split<true>(a, n_seg, *split, n_sub, (cudaStream_t)st);
-  return launch_scan<true>(a, n_seg, (cudaStream_t)st);
+  if (split) return launch_split<kSsd>(a, n_seg, *split, n_sub, (cudaStream_t)st);
+  return launch_scan<kSsd>(a, n_seg, (cudaStream_t)st);
 }
 
 extern "C" int prl_ssd_scan(const float* P, int64_t ldp, int32_t off_dt, const float* xbc, int64_t ld_xbc,
@@ -616,4 +641,54 @@ extern "C" int prl_ssd_scan_split(const float* P, int64_t ldp, int32_t off_dt, c
   PRL_CHECK_ARG(split_args(p, seg_sub0, seg_nsub, sub_start, sub_len, n_sub, scratch, cdec), "prl_ssd_scan_split: bad piece tables");
   return ssd_scan_impl(P, ldp, off_dt, xbc, ld_xbc, dt_bias, a_log, skip, heads, groups, n_state, dv, sub_start, sub_len,
                        seg_slot, n_seg, state, out, ld_out, &p, n_sub, st);
+}
+
+// ---- SCALAR front end: S_t = a_t S_(t-1) + b_t k_t v_t^T, o_t = q_scale * S_t^T q_t ----------------------------------
+// q, k: columns off_q / off_k (+ head * dk) of P; values: columns off_x (+ head * dv) of `xval` (which may be P).
+// gates != NULL: (a_t, b_t) = gates[row * ld_g + off_g + 2 * head + {0, 1}]; otherwise a_t = const_decay[head], b_t = 1.
+static int decay_scan_impl(const float* P, int64_t ldp, int32_t off_q, int32_t off_k, float q_scale, const float* xval,
+                           int64_t ld_x, int32_t off_x, const float* gates, int64_t ld_g, int32_t off_g,
+                           const float* const_decay, int32_t heads, int32_t dk, int32_t dv, const int32_t* seg_start,
+                           const int32_t* seg_len, const int32_t* seg_slot, int32_t n_seg, float* state, float* out,
+                           int64_t ld_out, const SplitArgs* split, int32_t n_sub, prl_stream_t st) {
+  PRL_CHECK_ARG(P && xval && (gates || const_decay) && seg_start && seg_len && seg_slot && state && out,
+                "prl_decay_scan: NULL argument");
+  PRL_CHECK_ARG(heads >= 1 && dk >= 1 && dk <= 256 && dv >= 1 && n_seg >= 1 && n_seg <= 65535,
+                "prl_decay_scan: bad shape (heads=%d dk=%d dv=%d, dk at most 256)", heads, dk, dv);
+  ScanArgs a = {};
+  a.seg_start = seg_start; a.seg_len = seg_len; a.seg_slot = seg_slot;
+  a.heads = heads; a.dk = dk; a.dv = dv;
+  a.state = state; a.state_slot_stride = prl_lin_scan_state_floats(heads, dk, dv);
+  a.out = out; a.ld_out = ld_out;
+  a.kvec = P; a.ld_k = ldp; a.off_k = off_k;
+  a.qvec = P; a.ld_q = ldp; a.off_q = off_q;
+  a.xval = xval; a.ld_x = ld_x; a.off_x = off_x;
+  a.q_scale = q_scale;
+  a.dt_raw = gates; a.ld_dt = ld_g; a.off_dt = off_g; a.groups = heads;
+  a.a_log = const_decay;
+  if (split) return launch_split<kScalar>(a, n_seg, *split, n_sub, (cudaStream_t)st);
+  return launch_scan<kScalar>(a, n_seg, (cudaStream_t)st);
+}
+
+extern "C" int prl_decay_scan(const float* P, int64_t ldp, int32_t off_q, int32_t off_k, float q_scale, const float* xval,
+                              int64_t ld_x, int32_t off_x, const float* gates, int64_t ld_g, int32_t off_g,
+                              const float* const_decay, int32_t heads, int32_t dk, int32_t dv, const int32_t* seg_start,
+                              const int32_t* seg_len, const int32_t* seg_slot, int32_t n_seg, float* state, float* out,
+                              int64_t ld_out, prl_stream_t st) {
+  return decay_scan_impl(P, ldp, off_q, off_k, q_scale, xval, ld_x, off_x, gates, ld_g, off_g, const_decay, heads, dk, dv,
+                         seg_start, seg_len, seg_slot, n_seg, state, out, ld_out, nullptr, 0, st);
+}
+
+// The same with every segment cut into side-by-side pieces (see prl_gla_scan_split for the tables).
+extern "C" int prl_decay_scan_split(const float* P, int64_t ldp, int32_t off_q, int32_t off_k, float q_scale,
+                                    const float* xval, int64_t ld_x, int32_t off_x, const float* gates, int64_t ld_g,
+                                    int32_t off_g, const float* const_decay, int32_t heads, int32_t dk, int32_t dv,
+                                    const int32_t* seg_slot, int32_t n_seg, const int32_t* seg_sub0,
+                                    const int32_t* seg_nsub, const int32_t* sub_start, const int32_t* sub_len,
+                                    int32_t n_sub, float* scratch, float* cdec, float* state, float* out, int64_t ld_out,
+                                    prl_stream_t st) {
+  SplitArgs p;
+  PRL_CHECK_ARG(split_args(p, seg_sub0, seg_nsub, sub_start, sub_len, n_sub, scratch, cdec), "prl_decay_scan_split: bad piece tables");
+  return decay_scan_impl(P, ldp, off_q, off_k, q_scale, xval, ld_x, off_x, gates, ld_g, off_g, const_decay, heads, dk, dv,
+                         sub_start, sub_len, seg_slot, n_seg, state, out, ld_out, &p, n_sub, st);
 }

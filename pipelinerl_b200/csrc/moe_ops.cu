@@ -1,0 +1,239 @@
+// Routed feed-forward (mixture of experts) over a packed batch of n token rows, without a host round trip: the number
+// of rows each expert gets stays on the device, so the whole layer can sit in a CUDA graph.
+//
+//   1. route:  per row, the `top` experts with the largest router logits (ties: the lower index), each with the weight
+//              sigmoid(logit) or softmax over the chosen; choice c of row t is the PAIR c * n + t.
+//   2. group:  a stable counting sort of the pairs by expert (one CTA): perm[s] = pair at sorted place s, and a table
+//              of row tiles (expert, first sorted place, rows <= 64) that the GEMMs walk; its length stays on the device.
+//   3. grouped GEMM (twice):  C[row] = A[row'] * W_e^T for every tile, W_e = W + e * expert_stride.  The first product
+//              reads the token's row (perm[s] % n) and writes sorted rows; the second reads sorted rows and writes
+//              pair rows, i.e. `top` slices [top][n][width] that the sublayer's closing kernel adds up.
+//   4. gated activation of an expert with the pair's weight folded in: the weight multiplies the expert's INPUT, and
+//              the two first projections are linear, so gate and up are scaled after the product (in fp32).
+//
+// The GEMM is the CUDA-core kernel of gemm_any.cu with a row indirection: every output element is summed by one thread
+// in ascending k, so a token's result does not depend on which rows share its tile.
+#include "prl_common.cuh"
+
+namespace prl {
+namespace {
+
+constexpr int kTile = 64;
+constexpr int kStepK = 16;
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
+
+// one warp per row; E up to 32 * kMaxPerLane
+constexpr int kMaxPerLane = 32;
+__global__ void moe_route_kernel(const float* __restrict__ logits, int64_t ld, int n, int E, int top, int softmax_weights,
+                                 int32_t* __restrict__ sel, float* __restrict__ wsel) {
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= n) return;
+  const float* z = logits + (int64_t)t * ld;
+  uint32_t taken = 0;            // bit j: expert lane + 32 j already chosen
+  float zsel_max = 0.f, denom = 0.f;
+  for (int c = 0; c < top; ++c) {
+    float best = -INFINITY;
+    int arg = 0x7fffffff;
+    for (int j = 0; j < kMaxPerLane; ++j) {
+      const int e = lane + 32 * j;
+      if (e >= E) break;
+      if (taken >> j & 1u) continue;
+      const float v = z[e];
+      if (v > best) { best = v; arg = e; }        // ascending e: the lower index wins a tie inside a lane
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+      if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+    }
+    if ((arg & 31) == lane) taken |= 1u << (arg >> 5);
+    if (c == 0) zsel_max = best;
+    denom += expf(best - zsel_max);
+    if (lane == 0) {
+      sel[(int64_t)c * n + t] = arg;
+      wsel[(int64_t)c * n + t] = softmax_weights ? expf(best - zsel_max) : sigmoid_f(best);
+    }
+  }
+  if (softmax_weights && lane == 0)
+    for (int c = 0; c < top; ++c) wsel[(int64_t)c * n + t] /= denom;
+}
+
+// meta[0] = number of tiles; tiles[3 * i + {0, 1, 2}] = expert, first sorted place, rows
+__global__ void __launch_bounds__(1024) moe_group_kernel(const int32_t* __restrict__ sel, int pairs, int E,
+                                                         int32_t* __restrict__ perm, int32_t* __restrict__ meta,
+                                                         int32_t* __restrict__ tiles) {
+  pdl_wait();
+  extern __shared__ int32_t cnt[];      // [E] counts, then [E] offsets
+  int32_t* off = cnt + E;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5;
+  for (int e = tid; e < E; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int p = tid; p < pairs; p += blockDim.x) atomicAdd(&cnt[sel[p]], 1);
+  __syncthreads();
+  if (tid == 0) {
+    int at = 0, nt = 0;
+    for (int e = 0; e < E; ++e) {
+      off[e] = at;
+      for (int r0 = 0; r0 < cnt[e]; r0 += kTile) {
+        tiles[3 * nt] = e;
+        tiles[3 * nt + 1] = at + r0;
+        tiles[3 * nt + 2] = min(kTile, cnt[e] - r0);
+        ++nt;
+      }
+      at += cnt[e];
+    }
+    meta[0] = nt;
+  }
+  __syncthreads();
+  for (int e = warp; e < E; e += nw) {     // stable: pairs of an expert keep their order
+    int at = off[e];
+    for (int p0 = 0; p0 < pairs; p0 += 32) {
+      const int p = p0 + lane;
+      const bool mine = p < pairs && sel[p] == e;
+      const uint32_t mask = __ballot_sync(0xffffffffu, mine);
+      if (mine) perm[at + __popc(mask & ((1u << lane) - 1u))] = p;
+      at += __popc(mask);
+    }
+  }
+}
+
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(256) moe_gemm_kernel(const TA* __restrict__ A, int64_t lda, int a_mod,
+                                                       const TW* __restrict__ W, int64_t expert_stride, int64_t ldw,
+                                                       const int32_t* __restrict__ perm, const int32_t* __restrict__ meta,
+                                                       const int32_t* __restrict__ tiles, int N, int K,
+                                                       float* __restrict__ C, int64_t ldc, int c_perm) {
+  pdl_wait();
+  const int tile = blockIdx.y;
+  if (tile >= meta[0]) return;
+  __shared__ float As[kStepK][kTile + 4];
+  __shared__ float Ws[kStepK][kTile + 4];
+  __shared__ int32_t a_row[kTile], c_row[kTile];
+  const int e = tiles[3 * tile], s0 = tiles[3 * tile + 1], M = tiles[3 * tile + 2];
+  const int tid = threadIdx.x;
+  if (tid < kTile) {
+    const int s = s0 + min(tid, M - 1);
+    const int p = perm[s];
+    a_row[tid] = a_mod > 0 ? p % a_mod : s;
+    c_row[tid] = c_perm ? p : s;
+  }
+  __syncthreads();
+  const TW* We = W + (int64_t)e * expert_stride;
+  const int n0 = blockIdx.x * kTile;
+  const int tm = (tid / 16) * 4, tn = (tid % 16) * 4;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  const int lr = tid / 4;          // 0..63
+  const int lk = (tid % 4) * 4;    // 0,4,8,12
+  const int64_t arow = a_row[lr];
+  for (int k0 = 0; k0 < K; k0 += kStepK) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int k = k0 + lk + j;
+      const int nn = n0 + lr;
+      As[lk + j][lr] = (lr < M && k < K) ? to_f32(A[arow * lda + k]) : 0.f;
+      Ws[lk + j][lr] = (nn < N && k < K) ? to_f32(We[(int64_t)nn * ldw + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < kStepK; ++kk) {
+      float a[4], w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[kk][tm + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) w[j] = Ws[kk][tn + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (tm + i >= M) continue;
+    const int64_t row = c_row[tm + i];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int nn = n0 + tn + j;
+      if (nn < N) C[row * ldc + nn] = acc[i][j];
+    }
+  }
+}
+
+// act[s] = g * sigmoid(beta g) * (u + 1),  g = min(w * gate, lim), u = clamp(w * up, -lim, lim),  w = wsel[perm[s]]
+template <typename T>
+__global__ void moe_glu_kernel(const float* __restrict__ gu, int64_t ld, int F, const int32_t* __restrict__ perm,
+                               const float* __restrict__ wsel, float lim, float beta, T* __restrict__ out) {
+  pdl_wait();
+  const int64_t s = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= F) return;
+  const float w = wsel[perm[s]];
+  const float g = fminf(w * gu[s * ld + c], lim);
+  const float u = fminf(fmaxf(w * gu[s * ld + F + c], -lim), lim);
+  out[s * F + c] = T(g * sigmoid_f(beta * g) * (u + 1.f));
+}
+
+}  // namespace
+}  // namespace prl
+
+using namespace prl;
+typedef __nv_bfloat16 bf16;
+
+extern "C" int64_t prl_moe_max_tiles(int64_t pairs, int32_t experts) { return (pairs + kTile - 1) / kTile + experts; }
+
+extern "C" int prl_moe_route(const float* logits, int64_t ld, int32_t n, int32_t experts, int32_t top,
+                             int32_t softmax_weights, int32_t* sel, float* wsel, int32_t* perm, int32_t* meta,
+                             int32_t* tiles, prl_stream_t st) {
+  PRL_CHECK_ARG(logits && sel && wsel && perm && meta && tiles, "prl_moe_route: NULL argument");
+  PRL_CHECK_ARG(n >= 1 && experts >= 1 && experts <= 32 * kMaxPerLane && top >= 1 && top <= experts && ld >= experts,
+                "prl_moe_route: bad shape (experts=%d top=%d; at most %d experts)", experts, top, 32 * kMaxPerLane);
+  cudaStream_t s = (cudaStream_t)st;
+  PRL_CUDA(launch_pdl(moe_route_kernel, dim3((n + 7) / 8), dim3(256), (size_t)0, s, logits, ld, n, experts, top, softmax_weights, sel, wsel));
+  PRL_LAUNCH_CHECK();
+  PRL_CUDA(launch_pdl(moe_group_kernel, dim3(1), dim3(1024), (size_t)(2 * experts * sizeof(int32_t)), s, (const int32_t*)sel, n * top, experts, perm, meta, tiles));
+  PRL_LAUNCH_CHECK();
+  return PRL_OK;
+}
+
+extern "C" int prl_moe_gemm(const void* A, int32_t a_is_f32, int64_t lda, int32_t a_mod, const void* W, int32_t w_is_f32,
+                            int64_t expert_stride, int64_t ldw, const int32_t* perm, const int32_t* meta,
+                            const int32_t* tiles, int64_t max_tiles, int64_t N, int64_t K, float* C, int64_t ldc,
+                            int32_t c_perm, prl_stream_t st) {
+  PRL_CHECK_ARG(A && W && perm && meta && tiles && C, "prl_moe_gemm: NULL argument");
+  PRL_CHECK_ARG(max_tiles >= 1 && max_tiles <= 65535 && N >= 1 && K >= 1 && lda >= K && ldw >= K && ldc >= N && a_mod >= 0,
+                "prl_moe_gemm: bad shape (tiles=%lld N=%lld K=%lld)", (long long)max_tiles, (long long)N, (long long)K);
+  dim3 grid((unsigned)((N + kTile - 1) / kTile), (unsigned)max_tiles);
+  cudaStream_t s = (cudaStream_t)st;
+#define PRL_MG(TA, TW) PRL_CUDA(launch_pdl((moe_gemm_kernel<TA, TW>), grid, dim3(256), (size_t)0, s, (const TA*)A, lda, a_mod, (const TW*)W, \
+                                           expert_stride, ldw, perm, meta, tiles, (int)N, (int)K, C, ldc, c_perm))
+  if (a_is_f32 && w_is_f32) PRL_MG(float, float);
+  else if (a_is_f32) PRL_MG(float, bf16);
+  else if (w_is_f32) PRL_MG(bf16, float);
+  else PRL_MG(bf16, bf16);
+#undef PRL_MG
+  PRL_LAUNCH_CHECK();
+  return PRL_OK;
+}
+
+extern "C" int prl_moe_glu(const float* gate_up, int64_t ld, int64_t pairs, int32_t F, const int32_t* perm,
+                           const float* wsel, float limit, float beta, void* out, int32_t f32, prl_stream_t st) {
+  PRL_CHECK_ARG(gate_up && perm && wsel && out && pairs >= 1 && F >= 1 && ld >= 2 * (int64_t)F, "prl_moe_glu: bad argument");
+  dim3 grid((unsigned)pairs, (F + 255) / 256);
+  if (f32) PRL_CUDA(launch_pdl(moe_glu_kernel<float>, grid, dim3(256), (size_t)0, (cudaStream_t)st, gate_up, ld, F, perm, wsel, limit, beta, (float*)out));
+  else PRL_CUDA(launch_pdl(moe_glu_kernel<bf16>, grid, dim3(256), (size_t)0, (cudaStream_t)st, gate_up, ld, F, perm, wsel, limit, beta, (bf16*)out));
+  PRL_LAUNCH_CHECK();
+  return PRL_OK;
+}

@@ -5,8 +5,13 @@ conf/base.yaml:59-73); this module is how such a family runs on `engine.EngineCo
 scheduler, sampler and CUDA graph are shared with the Qwen2 engine, and this file adds only the layer program.
 
 `HybridConfig` is a list of layer specs; every size and constant is a field, nothing is fixed to one model.  The
-"Povurax" architecture is one parser of that config (`HybridConfig.from_povurax`): another design built from the same
-mixers needs a parser, not new kernels.
+"Povurax" and "Belelorn" architectures are two parsers of that config (`HybridConfig.from_povurax`, `.from_belelorn`):
+another design built from the same mixers needs a parser, not new kernels.  Belelorn adds: a matrix-memory LSTM mixer
+(stabilised exponential gates), softmax attention whose values are its keys (per-head unit norms, tanh-capped scores,
+a sliding window that keeps the first tokens) beside lightning attention (one fixed decay per head), every sublayer
+normed on its input AND its output with gains kept as offsets from one, squared-ReLU and routed (mixture-of-experts)
+feed-forwards, a block of layers that runs several times on the same weights with a cache and state per pass, and
+sinusoidal positions added to the embedding.
 
 Numerics: the residual stream, every norm, softmax, router-like gate, decay, step size and recurrent state are fp32.
 GEMM operands and the KV cache are bf16, or fp32 when the arena is fp32 (the true-fp32 mode: CUDA-core GEMMs with fp32
@@ -34,6 +39,43 @@ class AttnSpec:
     rot_dims: int       # leading channels of each head that are rotated (interleaved pairs)
     rot_base: float
     scale: float        # score = (q . k) * scale
+    # what follows is off / zero for a plain attention layer
+    softcap: float = 0.0        # > 0: score <- softcap * tanh(score / softcap)
+    window: int = 0             # > 0: a query sees only the last `window` positions (itself included) ...
+    keep_first: int = 0         # ... and the first `keep_first` tokens of the sequence
+    head_norm: bool = False     # q and k divided by their RMS per head, no gain (instead of one gained norm over all heads)
+    bias: bool = False          # q and k projections have biases
+    value_is_key: bool = False  # no value projection: the value is the key as projected (before its norm)
+    gate: bool = True           # sigmoid output gate from its own projection
+
+
+@dataclass(frozen=True)
+class LightningSpec:
+    """Linear attention S <- decay_h S + k v^T, o = S^T q, with SiLU on q, k, v and one fixed decay per head."""
+    heads: int
+    dim: int
+    vdim: int
+    decay: tuple
+
+
+@dataclass(frozen=True)
+class MlstmSpec:
+    """Matrix-memory LSTM cell: exponential input gate, sigmoid forget gate, both soft-capped, running stabiliser."""
+    heads: int
+    dim: int
+    vdim: int
+    gate_cap: float
+    den_eps: float = 1e-6
+
+
+@dataclass(frozen=True)
+class MoeSpec:
+    experts: int
+    top: int
+    ff: int
+    limit: float
+    shared_ff: int = 0          # 0: no shared expert
+    shared_limit: float = 0.0
 
 
 @dataclass(frozen=True)
@@ -72,11 +114,13 @@ class MlpSpec:
     ff: int
     limit: float
     beta: float = 1.702  # g * sigmoid(beta * g)
+    kind: str = "glu"    # "glu": clamped gated unit | "relu2": W_down relu(W_up h)^2 | "moe": routed experts (+ a shared one)
+    moe: MoeSpec | None = None
 
 
 @dataclass(frozen=True)
 class LayerSpec:
-    kind: str                       # "gla" | "parallel"
+    kind: str                       # "gla" | "parallel" (attention || state space) | "parallel_lin" (attention || lightning) | "mlstm"
     weights_of: int                 # index of the layer whose tensors this layer uses (its own index if it has its own)
     gla: GlaSpec | None = None
     attn: AttnSpec | None = None
@@ -84,6 +128,10 @@ class LayerSpec:
     left_scale: float = 1.0
     right_scale: float = 1.0
     mlp: MlpSpec | None = None
+    lin: LightningSpec | None = None
+    mlstm: MlstmSpec | None = None
+    sandwich: bool = False          # norms before AND after each sublayer (norm1, norm1b, norm2, norm2b) instead of after only
+    opens_pass: int | None = None   # this run opens pass t of a repeated block: x <- W_loop [x; x0] + step[t] comes first
 
 
 @dataclass(frozen=True)
@@ -92,7 +140,11 @@ class HybridConfig:
     width: int
     eps: float
     embed_scale: float
-    layers: tuple
+    layers: tuple                   # one LayerSpec per layer RUN (a repeated block is unrolled; runs share tensors by weights_of)
+    positions: str = "none"         # "sinusoid": sin / cos of position * 10000^(-2i/width) added to the embedding
+    logit_scale: float = 1.0
+    norm_offset: float = 0.0        # gains of the width norms are stored as offsets from this value
+    loop_times: int = 0             # passes of the repeated block (rows of `loop.step`); 0: no such block
 
     @property
     def head_rows(self) -> int:
@@ -155,8 +207,72 @@ class HybridConfig:
         cfg.validate()
         return cfg
 
+    # ---- the "Belelorn" reading of config.json ---------------------------------------------------------------------
+    @staticmethod
+    def from_belelorn(d: dict, tensor_shapes: dict | None = None) -> "HybridConfig":
+        """config.json of a Belelorn checkpoint.  `loop` = {start, stop, times}: layers start .. stop-1 run `times` times
+        in a row on the same tensors; every pass is a run of its own here (own cache and state)."""
+        specs = []
+        for i, L in enumerate(d["layers"]):
+            m, mlp = L["mixer"], None
+            f = L.get("mlp")
+            if f is not None:
+                kind = f.get("kind", "dense")
+                if kind == "dense":
+                    mlp = MlpSpec(ff=int(f["ff"]), limit=0.0, kind="relu2")
+                elif kind == "moe":
+                    sh = f.get("shared")
+                    moe = MoeSpec(int(f["router"]["experts"]), int(f["router"]["top"]), int(f["expert"]["ff"]),
+                                  float(f["expert"]["limit"]), int(sh["ff"]) if sh else 0, float(sh["limit"]) if sh else 0.0)
+                    mlp = MlpSpec(ff=moe.shared_ff, limit=moe.shared_limit, kind="moe", moe=moe)
+                else:
+                    raise ValueError(f"layer {i}: unknown feed-forward kind {kind!r}")
+            if L["type"] == "mlstm":
+                specs.append(dict(kind="mlstm", mlp=mlp, mlstm=MlstmSpec(int(m["heads"]), int(m["dim"]), int(m["vdim"]),
+                                                                         float(m["gate_cap"]))))
+            elif L["type"] == "parallel":
+                a, r = m["left"], m["right"]
+                mask = a.get("mask") or {}
+                attn = AttnSpec(int(a["heads"]), int(a.get("kv_heads", a["heads"])), int(a["dim"]), int(a.get("vdim", a["dim"])),
+                                0, 10000.0, float(a["scale"]), softcap=float(a.get("softcap", 0.0)),
+                                window=int(mask.get("size", 0)), keep_first=int(mask.get("keep_first", 0)), head_norm=True,
+                                bias=True, value_is_key=True, gate=False)
+                lin = LightningSpec(int(r["heads"]), int(r["dim"]), int(r["vdim"]), tuple(float(v) for v in r["decay"]))
+                specs.append(dict(kind="parallel_lin", mlp=mlp, attn=attn, lin=lin, left_scale=0.5, right_scale=0.5))
+            else:
+                raise ValueError(f"layer {i}: unknown mixer type {L['type']!r}")
+        n, loop = len(specs), d.get("loop")
+        runs = [(i, None) for i in range(n)]
+        times = 0
+        if loop:
+            a, b, times = int(loop["start"]), int(loop["stop"]), int(loop["times"])
+            if not (0 <= a < b <= n and times >= 1):
+                raise ValueError(f"bad loop {loop}")
+            runs = [(i, None) for i in range(a)]
+            for t in range(times):
+                runs += [(i, t if i == a else None) for i in range(a, b)]
+            runs += [(i, None) for i in range(b, n)]
+        layers = tuple(LayerSpec(weights_of=i, sandwich=True, opens_pass=t, **specs[i]) for i, t in runs)
+        cfg = HybridConfig(int(d["vocab"]), int(d["width"]), float(d["norm"]["eps"]), 1.0, layers, positions="sinusoid",
+                           logit_scale=float(d.get("logit_scale", 1.0)), norm_offset=1.0, loop_times=times)
+        cfg.validate()
+        return cfg
+
     def validate(self) -> None:
         for i, L in enumerate(self.layers):
+            if L.kind == "mlstm":
+                if L.mlstm.dim > 256 or L.mlstm.gate_cap <= 0:
+                    raise ValueError(f"layer run {i}: bad matrix-memory geometry {L.mlstm}")
+            elif L.kind == "parallel_lin":
+                a, r = L.attn, L.lin
+                if a.heads % a.kv_heads or (a.value_is_key and a.vdim != a.dim) or a.dim > 512 or a.vdim > 256:
+                    raise ValueError(f"layer run {i}: bad attention geometry {a}")
+                if len(r.decay) != r.heads or r.dim > 256:
+                    raise ValueError(f"layer run {i}: bad lightning-attention geometry {r}")
+            if L.mlp is not None and L.mlp.kind == "moe" and not 1 <= L.mlp.moe.top <= L.mlp.moe.experts <= 1024:
+                raise ValueError(f"layer run {i}: bad router {L.mlp.moe}")
+            if L.kind in ("mlstm", "parallel_lin"):
+                continue
             if L.kind == "parallel":
                 a, s = L.attn, L.ssd
                 if a.heads % a.kv_heads or a.rot_dims % 2 or a.rot_dims > a.dim:
@@ -170,7 +286,12 @@ class HybridConfig:
 
     # ---- the parameter arena: fused tensors in kernel order ---------------------------------------------------------
     def _own(self):
-        return [(i, L) for i, L in enumerate(self.layers) if L.weights_of == i]
+        """(tensor prefix index, spec) of every layer that has tensors of its own, in index order.  Runs that share
+        tensors (weights_of) have the same sizes, so the first of them stands for all."""
+        own: dict[int, LayerSpec] = {}
+        for L in self.layers:
+            own.setdefault(L.weights_of, L)
+        return sorted(own.items())
 
     def fused_shapes(self) -> list[tuple[str, tuple[int, ...]]]:
         W, out = self.width, []
@@ -181,6 +302,18 @@ class HybridConfig:
                 nq, nv = g.heads * g.dim, g.heads * g.vdim
                 out += [(p + "mix.in", (2 * nq + 2 * nv + g.rank, W)), (p + "mix.a2", (nq, g.rank)),
                         (p + "mix.a2.b", (nq,)), (p + "mix.norm", (g.vdim,)), (p + "mix.o", (W, nv))]
+            elif L.kind == "mlstm":
+                m = L.mlstm
+                nq, nv = m.heads * m.dim, m.heads * m.vdim
+                out += [(p + "mix.in", (2 * nq + 2 * nv + 2 * m.heads, W)), (p + "mix.gate.b", (2 * m.heads,)),
+                        (p + "mix.norm", (nv,)), (p + "mix.o", (W, nv))]
+            elif L.kind == "parallel_lin":
+                a, r = L.attn, L.lin
+                nq, nk = a.heads * a.dim, a.kv_heads * a.dim
+                rq, rv = r.heads * r.dim, r.heads * r.vdim
+                out += [(p + "mix.in", (nq + nk + 2 * rq + 2 * rv, W)), (p + "mix.left.b", (nq + nk,)),
+                        (p + "mix.left.o", (W, a.heads * a.vdim)), (p + "mix.right.norm", (rv,)),
+                        (p + "mix.right.o", (W, rv)), (p + "mix.left.out", (W,)), (p + "mix.right.out", (W,))]
             else:
                 a, s = L.attn, L.ssd
                 nq, nk, nv = a.heads * a.dim, a.kv_heads * a.dim, a.kv_heads * a.vdim
@@ -192,8 +325,24 @@ class HybridConfig:
                         (p + "mix.right.D", (s.heads,)), (p + "mix.right.norm", (s.inner,)),
                         (p + "mix.right.o", (W, s.inner))]
             out.append((p + "norm1", (W,)))
+            if L.sandwich:
+                out.append((p + "norm1b", (W,)))
             if L.mlp is not None:
-                out += [(p + "mlp.gate_up", (2 * L.mlp.ff, W)), (p + "mlp.down", (W, L.mlp.ff)), (p + "norm2", (W,))]
+                f = L.mlp
+                if f.kind == "relu2":
+                    out += [(p + "mlp.up", (f.ff, W)), (p + "mlp.down", (W, f.ff))]
+                else:
+                    if f.kind == "moe":
+                        e = f.moe
+                        out += [(p + "mlp.router", (e.experts, W)), (p + "mlp.experts.gate_up", (e.experts * 2 * e.ff, W)),
+                                (p + "mlp.experts.down", (e.experts * W, e.ff))]
+                    if f.ff > 0:
+                        out += [(p + "mlp.gate_up", (2 * f.ff, W)), (p + "mlp.down", (W, f.ff))]
+                out.append((p + "norm2", (W,)))
+                if L.sandwich:
+                    out.append((p + "norm2b", (W,)))
+        if self.loop_times:
+            out += [("loop.in", (W, 2 * W)), ("loop.step", (self.loop_times, W))]
         out += [("embed", (self.vocab_size, W)), ("final.norm", (W,)), ("head", (self.vocab_size, W))]
         return out
 
@@ -215,6 +364,24 @@ class HybridConfig:
                                     (p + "mix.a1", g.rank)])
                 for name, n in (("mix.a2", nq), ("mix.a2.b", nq), ("mix.norm", g.vdim), ("mix.o", self.width)):
                     m[p + name] = (p + name, 0, n)
+            elif L.kind == "mlstm":
+                c = L.mlstm
+                nq, nv = c.heads * c.dim, c.heads * c.vdim
+                rows(p + "mix.in", [(p + "mix.q", nq), (p + "mix.k", nq), (p + "mix.v", nv), (p + "mix.g", nv),
+                                    (p + "mix.i", c.heads), (p + "mix.f", c.heads)])
+                rows(p + "mix.gate.b", [(p + "mix.i.b", c.heads), (p + "mix.f.b", c.heads)])
+                m[p + "mix.norm"] = (p + "mix.norm", 0, nv)
+                m[p + "mix.o"] = (p + "mix.o", 0, self.width)
+            elif L.kind == "parallel_lin":
+                a, r = L.attn, L.lin
+                nq, nk = a.heads * a.dim, a.kv_heads * a.dim
+                rq, rv = r.heads * r.dim, r.heads * r.vdim
+                rows(p + "mix.in", [(p + "mix.left.q", nq), (p + "mix.left.k", nk), (p + "mix.right.q", rq),
+                                    (p + "mix.right.k", rq), (p + "mix.right.v", rv), (p + "mix.right.g", rv)])
+                rows(p + "mix.left.b", [(p + "mix.left.q.b", nq), (p + "mix.left.k.b", nk)])
+                for name, n in (("mix.left.o", self.width), ("mix.right.norm", rv), ("mix.right.o", self.width),
+                                ("mix.left.out", self.width), ("mix.right.out", self.width)):
+                    m[p + name] = (p + name, 0, n)
             else:
                 a, s = L.attn, L.ssd
                 nq, nk, nv = a.heads * a.dim, a.kv_heads * a.dim, a.kv_heads * a.vdim
@@ -226,10 +393,32 @@ class HybridConfig:
                                 ("mix.right.norm", s.inner), ("mix.right.o", self.width)):
                     m[p + name] = (p + name, 0, n)
             m[p + "norm1"] = (p + "norm1", 0, self.width)
+            if L.sandwich:
+                m[p + "norm1b"] = (p + "norm1b", 0, self.width)
             if L.mlp is not None:
-                rows(p + "mlp.gate_up", [(p + "mlp.gate", L.mlp.ff), (p + "mlp.up", L.mlp.ff)])
-                m[p + "mlp.down"] = (p + "mlp.down", 0, self.width)
+                f = L.mlp
+                if f.kind == "relu2":
+                    m[p + "mlp.up"] = (p + "mlp.up", 0, f.ff)
+                    m[p + "mlp.down"] = (p + "mlp.down", 0, self.width)
+                elif f.kind == "moe":
+                    e = f.moe
+                    m[p + "mlp.router"] = (p + "mlp.router", 0, e.experts)
+                    for k in range(e.experts):
+                        m[f"{p}mlp.e{k}.gate"] = (p + "mlp.experts.gate_up", k * 2 * e.ff, e.ff)
+                        m[f"{p}mlp.e{k}.up"] = (p + "mlp.experts.gate_up", k * 2 * e.ff + e.ff, e.ff)
+                        m[f"{p}mlp.e{k}.down"] = (p + "mlp.experts.down", k * self.width, self.width)
+                    if f.ff > 0:
+                        rows(p + "mlp.gate_up", [(p + "mlp.shared.gate", f.ff), (p + "mlp.shared.up", f.ff)])
+                        m[p + "mlp.shared.down"] = (p + "mlp.down", 0, self.width)
+                else:
+                    rows(p + "mlp.gate_up", [(p + "mlp.gate", f.ff), (p + "mlp.up", f.ff)])
+                    m[p + "mlp.down"] = (p + "mlp.down", 0, self.width)
                 m[p + "norm2"] = (p + "norm2", 0, self.width)
+                if L.sandwich:
+                    m[p + "norm2b"] = (p + "norm2b", 0, self.width)
+        if self.loop_times:
+            m["loop.in"] = ("loop.in", 0, self.width)
+            m["loop.step"] = ("loop.step", 0, self.loop_times)
         m["embed"] = ("embed", 0, self.vocab_size)
         m["final.norm"] = ("final.norm", 0, self.width)
         m["head"] = ("head", 0, self.vocab_size)
@@ -238,8 +427,12 @@ class HybridConfig:
     def init_param(self, name: str, view: torch.Tensor, gen: torch.Generator) -> None:
         """Random initialisation for benches and tests: unit gains, small biases, weights of std 1/sqrt(fan_in)."""
         leaf = name.split(".")[-1]
-        if leaf in ("norm", "norm1", "norm2") or name == "final.norm":
+        if leaf in ("norm1", "norm2", "norm1b", "norm2b") or name == "final.norm":
+            view.fill_(1.0 - self.norm_offset)
+        elif leaf in ("norm", "out"):
             view.fill_(1.0)
+        elif name == "loop.step":
+            view.copy_((torch.randn(view.shape, generator=gen, device=view.device) * 0.1).to(view.dtype))
         elif leaf == "A_log":
             view.copy_(torch.log(torch.linspace(1.0, 4.0, view.numel())).to(view.dtype))
         elif leaf in ("D",):
@@ -272,12 +465,26 @@ class _Rows:
         cfg, d, T = eng.cfg, eng.dev, eng.op_dtype
         W = cfg.width
         wide_p, wide_aux, wide_o, wide_o2, wide_q, wide_f = W, 1, 1, 1, 1, 1
+        wide_gate, moe_pairs, moe_ff, moe_experts = 0, 0, 1, 1     # mLSTM gate heads; routed pairs per row, expert width
         for L in cfg.layers:
             if L.kind == "gla":
                 g = L.gla
                 nq, nv = g.heads * g.dim, g.heads * g.vdim
                 wide_p = max(wide_p, 2 * nq + 2 * nv + g.rank)
                 wide_aux, wide_o = max(wide_aux, nq), max(wide_o, nv)
+            elif L.kind == "mlstm":
+                m = L.mlstm
+                nq, nv = m.heads * m.dim, m.heads * m.vdim
+                wide_p = max(wide_p, 2 * nq + 2 * nv + 2 * m.heads)
+                wide_aux = max(wide_aux, m.heads * (m.vdim + 1))
+                wide_o = max(wide_o, m.heads * (m.vdim + 1))
+                wide_gate = max(wide_gate, m.heads)
+            elif L.kind == "parallel_lin":
+                a, r = L.attn, L.lin
+                nq = a.heads * a.dim
+                wide_p = max(wide_p, nq + a.kv_heads * a.dim + 2 * r.heads * (r.dim + r.vdim))
+                wide_o, wide_q = max(wide_o, a.heads * a.vdim), max(wide_q, nq)
+                wide_o2 = max(wide_o2, r.heads * r.vdim)
             else:
                 a, s = L.attn, L.ssd
                 nq = a.heads * a.dim
@@ -286,6 +493,10 @@ class _Rows:
                 wide_o2, wide_q = max(wide_o2, s.inner), max(wide_q, nq)
             if L.mlp is not None:
                 wide_p, wide_f = max(wide_p, 2 * L.mlp.ff), max(wide_f, L.mlp.ff)
+                if L.mlp.kind == "moe":
+                    e = L.mlp.moe
+                    wide_p = max(wide_p, e.top * 2 * e.ff)
+                    moe_pairs, moe_ff, moe_experts = max(moe_pairs, e.top), max(moe_ff, e.ff), max(moe_experts, e.experts)
         f32 = dict(dtype=torch.float32, device=d)
         i32 = dict(dtype=torch.int32, device=d)
         self.n = n
@@ -303,6 +514,22 @@ class _Rows:
         self.y1 = torch.zeros(ny, **f32)
         self.q = torch.zeros(n * wide_q, dtype=T, device=d)
         self.act = torch.zeros(n * wide_f, dtype=T, device=d)
+        if cfg.loop_times:                                      # the embedding output and [x | x0], operand type
+            self.x0a = torch.zeros(n * W, dtype=T, device=d)
+            self.xcat = torch.zeros(n * 2 * W, dtype=T, device=d)
+        if wide_gate:                                           # mLSTM: (keep, take) per head and token, exp(-m)
+            self.gates = torch.zeros(n * 2 * wide_gate, **f32)
+            self.minv = torch.zeros(n * wide_gate, **f32)
+        if moe_pairs:                                           # routed feed-forward: pairs = choices x rows
+            pairs = n * moe_pairs
+            self.router = torch.zeros(n * moe_experts, **f32)
+            self.sel = torch.zeros(pairs, **i32)
+            self.wsel = torch.zeros(pairs, **f32)
+            self.perm = torch.zeros(pairs, **i32)
+            self.moe_meta = torch.zeros(4, **i32)
+            self.moe_tiles = torch.zeros(3 * int(eng.lib.prl_moe_max_tiles(pairs, moe_experts)), **i32)
+            self.moe_act = torch.zeros(pairs * moe_ff, dtype=T, device=d)
+            self.moe_out = torch.zeros(pairs * W, **f32)        # [choice][row][W]: summed by the sublayer's closing kernel
         self.tokens = torch.zeros(n, **i32)
         self.row_pos = torch.zeros(n, **i32)
         self.row_slot = torch.zeros(n, **i32)
@@ -315,8 +542,7 @@ class _Rows:
         if pieces:
             lib, st, dc = eng.lib, 1, 1
             for L in cfg.layers:
-                for heads, dk, dv in ([(L.gla.heads, L.gla.dim, L.gla.vdim)] if L.kind == "gla" else
-                                      [(L.ssd.heads, L.ssd.state, L.ssd.vdim)]):
+                for heads, dk, dv in eng.scan_geometry(L):
                     st = max(st, int(lib.prl_lin_scan_state_floats(heads, dk, dv)))
                     dc = max(dc, int(lib.prl_lin_scan_piece_decay_floats(heads, dk)))
             self.max_sub = n // eng.piece_tokens + 8
@@ -351,11 +577,29 @@ class HybridEngine(EngineCore):
         cfg, d, lib = self.cfg, self.dev, self.lib
         self.k_pool, self.v_pool, self.conv_state, self.ssd_state, self.gla_state, self.rot_freq = {}, {}, {}, {}, {}, {}
         self.tc_attn: dict[int, bool] = {}
+        self.lin_state, self.lin_decay, self.mlstm_state, self.mlstm_m = {}, {}, {}, {}
         for i, L in enumerate(cfg.layers):               # one cache / state per layer RUN, also where weights are shared
             if L.kind == "gla":
                 g = L.gla
                 n = int(lib.prl_lin_scan_state_floats(g.heads, g.dim, g.vdim))
                 self.gla_state[i] = self.states.add(f"l{i}.gla", (n,))
+            elif L.kind == "mlstm":
+                m = L.mlstm                              # matrix memory with the normaliser as one more value column, and m
+                n = int(lib.prl_lin_scan_state_floats(m.heads, m.dim, m.vdim + 1))
+                self.mlstm_state[i] = self.states.add(f"l{i}.mlstm", (n,))
+                self.mlstm_m[i] = self.states.add(f"l{i}.mlstm.m", (m.heads,))
+            elif L.kind == "parallel_lin":
+                a, r = L.attn, L.lin
+                pair = torch.zeros(2, self.n_pages, a.kv_heads, PAGE_SIZE, a.dim, dtype=self.op_dtype, device=d)
+                if a.dim == a.vdim:
+                    self.k_pool[i], self.v_pool[i] = pair[0], pair[1]
+                else:
+                    self.k_pool[i] = pair[0]
+                    self.v_pool[i] = torch.zeros(self.n_pages, a.kv_heads, PAGE_SIZE, a.vdim, dtype=self.op_dtype, device=d)
+                self.tc_attn[i] = False                  # window, kept first tokens and capped scores: the any-geometry kernel
+                n = int(lib.prl_lin_scan_state_floats(r.heads, r.dim, r.vdim))
+                self.lin_state[i] = self.states.add(f"l{i}.lin", (n,))
+                self.lin_decay[i] = torch.tensor(r.decay, dtype=torch.float32, device=d)
             else:
                 a, s = L.attn, L.ssd
                 if a.dim == a.vdim:    # K and V pools adjacent: [2][page][kv head][64][d], the layout of the Qwen2 engine's pool
@@ -377,8 +621,11 @@ class HybridEngine(EngineCore):
         # fp32 copies of the small parameter vectors (gains, biases, taps, per-head constants): exact for bf16 weights
         self.vec: dict[str, torch.Tensor] = {}
         for name, shape in cfg.fused_shapes():
-            if len(shape) == 1 or name.endswith("mix.right.conv"):
+            if len(shape) == 1 or name.endswith("mix.right.conv") or name == "loop.step":
                 self.vec[name] = torch.zeros(shape, dtype=torch.float32, device=d)
+        if cfg.positions == "sinusoid":
+            W = cfg.width
+            self.pos_freq = torch.tensor([10000.0 ** (-2.0 * k / W) for k in range((W + 1) // 2)], dtype=torch.float64, device=d)
         self._on_arena_change()
         B = self.B
         self.attn_splits, ws = {}, 0
@@ -394,12 +641,29 @@ class HybridEngine(EngineCore):
         self._dec.seg[3].copy_(torch.arange(B, **i32))
 
     def _on_arena_change(self) -> None:
+        cfg = self.cfg
         for name, t in self.vec.items():
             t.copy_(self.arena.view(name).float())
+            if name == "final.norm" or name.split(".")[-1] in ("norm1", "norm1b", "norm2", "norm2b"):
+                if cfg.norm_offset:
+                    t.add_(cfg.norm_offset)              # gains stored as offsets
+        if cfg.logit_scale != 1.0:
+            self.vec["final.norm"].mul_(cfg.logit_scale)   # logits = head(norm(x)) * scale: folded into the last gain
+
+    @staticmethod
+    def scan_geometry(L) -> list:
+        """(heads, key size, value columns) of every matrix-state recurrence of a layer."""
+        if L.kind == "gla":
+            return [(L.gla.heads, L.gla.dim, L.gla.vdim)]
+        if L.kind == "mlstm":
+            return [(L.mlstm.heads, L.mlstm.dim, L.mlstm.vdim + 1)]
+        if L.kind == "parallel_lin":
+            return [(L.lin.heads, L.lin.dim, L.lin.vdim)]
+        return [(L.ssd.heads, L.ssd.state, L.ssd.vdim)]
 
     def kv_bytes_per_token(self) -> int:
         e = 4 if self.f32 else 2
-        return sum(L.attn.kv_heads * (L.attn.dim + L.attn.vdim) * e for L in self.cfg.layers if L.kind == "parallel")
+        return sum(L.attn.kv_heads * (L.attn.dim + L.attn.vdim) * e for L in self.cfg.layers if L.attn is not None)
 
     # ---- GEMM dispatch ------------------------------------------------------------------------------------------------
     def _mm(self, src: torch.Tensor, K: int, w_name: str, N: int, out: torch.Tensor, n: int, split: bool = False) -> int:
@@ -430,9 +694,21 @@ class HybridEngine(EngineCore):
         if n_sub:
             pieces = (R.seg_sub[0].data_ptr(), R.seg_sub[1].data_ptr(), R.sub[0].data_ptr(), R.sub[1].data_ptr(), n_sub,
                       R.scratch.data_ptr(), R.cdec.data_ptr())
+        segs = (seg_start, seg_len, seg_slot, ns)
         for i, L in enumerate(cfg.layers):
             w = f"l{L.weights_of}."
-            if L.kind == "gla":
+            if L.opens_pass is not None:
+                # a pass of the repeated block opens: x <- W_loop [x; x0] + step[pass], then the first layer's input norm
+                _lib.check(lib.prl_concat_rows(xa, R.x0a.data_ptr(), n, W, R.xcat.data_ptr(), f32, st))
+                k0 = self._mm(R.xcat, 2 * W, "loop.in", W, R.y0, n, split=True)
+                self._close(R, n, R.y0, k0, bias=vec["loop.step"][L.opens_pass], add=False, next_gain=self._pre_gain(i))
+            elif i == 0 and L.sandwich:
+                _lib.check(lib.prl_rmsnorm_rows(x, None, vec[w + "norm1"].data_ptr(), eps, n, W, xa, f32, st))
+            if L.kind == "mlstm":
+                self._mlstm_mixer(R, n, i, L, w, segs, pieces if n_sub else None)
+            elif L.kind == "parallel_lin":
+                self._attn_lightning_mixer(R, n, i, L, w, segs, pieces if n_sub else None, max_q, row_pos, seg_pos0)
+            elif L.kind == "gla":
                 g = L.gla
                 nq, nv = g.heads * g.dim, g.heads * g.vdim
                 ld = 2 * nq + 2 * nv + g.rank
@@ -513,31 +789,170 @@ class HybridEngine(EngineCore):
                 _lib.check(lib.prl_postnorm_residual(R.y0.data_ptr(), W, L.left_scale, k0, R.y1.data_ptr(), W, L.right_scale, k1,
                                                      vec[w + "norm1"].data_ptr(), eps, n, W, x, xa, f32, st))
             if L.mlp is not None:
-                F = L.mlp.ff
-                tc = not (self.f32 or self.force_plain_gemm or W % 8 or W < 64 or self.unfused_glu)
-                if tc and n <= 128 and F % 64 == 0:
-                    # the clamped gate in the gate_up GEMM's epilogue (the Qwen2 step's SwiGLU-epilogue kernel): no [n, 2F] tile
-                    _lib.check(lib.prl_gemm_glu_clamped_decode(self.arena.ptr(w + "mlp.gate_up"), xa, n, F, W, L.mlp.limit,
-                                                               L.mlp.beta, R.act.data_ptr(), st))
-                elif tc and n > 128 and F % 128 == 0:
-                    _lib.check(lib.prl_gemm_glu_clamped_f32(xa, W, self.arena.ptr(w + "mlp.gate_up"), W, n, F, W, L.mlp.limit,
-                                                            L.mlp.beta, R.act.data_ptr(), F, st))
+                f = L.mlp
+                k0 = 0
+                if f.kind == "relu2":
+                    self._mm(R.xa, W, w + "mlp.up", f.ff, R.P, n)
+                    _lib.check(lib.prl_act_store(P, f.ff, n, f.ff, 0, R.act.data_ptr(), f32, st))
+                    k0 = self._mm(R.act, f.ff, w + "mlp.down", W, R.y0, n, split=True)
+                elif f.ff > 0:
+                    k0 = self._glu_ff(R, n, w, f)
+                routed = self._routed_ff(R, n, w, f.moe, f.beta) if f.kind == "moe" else None
+                if L.sandwich:
+                    y, ky = (R.y0, k0) if k0 else (routed, f.moe.top)
+                    y1, k1 = (routed, f.moe.top) if (k0 and routed is not None) else (None, 1)
+                    self._close(R, n, y, ky, y1=y1, k1=k1, post_gain=vec[w + "norm2b"], next_gain=self._next_gain(i, False))
                 else:
-                    self._mm(R.xa, W, w + "mlp.gate_up", 2 * F, R.P, n)
-                    _lib.check(lib.prl_glu_clamped(P, 2 * F, n, F, L.mlp.limit, L.mlp.beta, R.act.data_ptr(), f32, st))
-                k0 = self._mm(R.act, F, w + "mlp.down", W, R.y0, n, split=True)
-                _lib.check(lib.prl_postnorm_residual(R.y0.data_ptr(), W, 1.0, k0, None, 0, 0.0, 1, vec[w + "norm2"].data_ptr(),
-                                                     eps, n, W, x, xa, f32, st))
+                    _lib.check(lib.prl_postnorm_residual(R.y0.data_ptr(), W, 1.0, k0, None, 0, 0.0, 1, vec[w + "norm2"].data_ptr(),
+                                                         eps, n, W, x, xa, f32, st))
             if trace is not None:
                 trace.append(R.x[:n * W].view(n, W).clone())
+
+    # ---- pieces of the layer program shared by several layer kinds ------------------------------------------------------
+    def _pre_gain(self, i: int):
+        """Gain of the norm in front of run i's mixer (None: the mixer reads x as it is)."""
+        L = self.cfg.layers[i]
+        return self.vec[f"l{L.weights_of}.norm1"] if L.sandwich else None
+
+    def _next_gain(self, i: int, after_mixer: bool):
+        """Gain of the input norm of whatever reads x after this sublayer of run i: the run's feed-forward, the next
+        run's mixer, or nothing (the opening of a pass and the model's last norm read x itself)."""
+        L = self.cfg.layers[i]
+        if after_mixer and L.mlp is not None:
+            return self.vec[f"l{L.weights_of}.norm2"] if L.sandwich else None
+        if i + 1 < len(self.cfg.layers) and self.cfg.layers[i + 1].opens_pass is None:
+            return self._pre_gain(i + 1)
+        return None
+
+    def _close(self, R, n, y0, k0, gain0=None, s0=1.0, y1=None, k1=1, gain1=None, s1=1.0, post_gain=None, bias=None,
+               add=True, next_gain=None) -> None:
+        """prl_sublayer_close on the residual stream: branch norms, sum, output norm, residual, the next input norm."""
+        W = self.cfg.width
+        ptr = lambda t: None if t is None else t.data_ptr()
+        _lib.check(self.lib.prl_sublayer_close(y0.data_ptr(), W, k0, ptr(gain0), s0, ptr(y1), W, k1, ptr(gain1), s1,
+                                               ptr(post_gain), ptr(bias), int(add), ptr(next_gain), self.cfg.eps, n, W,
+                                               R.x.data_ptr(), R.xa.data_ptr(), int(self.f32), self._st))
+
+    def _glu_ff(self, R, n, w, f) -> int:
+        """Clamped gated unit l<w>.mlp.gate_up / .down on xa; returns the number of split-K slices left in R.y0."""
+        lib, st, W, F, f32 = self.lib, self._st, self.cfg.width, f.ff, int(self.f32)
+        xa, P = R.xa.data_ptr(), R.P.data_ptr()
+        tc = not (self.f32 or self.force_plain_gemm or W % 8 or W < 64 or self.unfused_glu)
+        if tc and n <= 128 and F % 64 == 0:
+            # the clamped gate in the gate_up GEMM's epilogue (the Qwen2 step's SwiGLU-epilogue kernel): no [n, 2F] tile
+            _lib.check(lib.prl_gemm_glu_clamped_decode(self.arena.ptr(w + "mlp.gate_up"), xa, n, F, W, f.limit, f.beta,
+                                                       R.act.data_ptr(), st))
+        elif tc and n > 128 and F % 128 == 0:
+            _lib.check(lib.prl_gemm_glu_clamped_f32(xa, W, self.arena.ptr(w + "mlp.gate_up"), W, n, F, W, f.limit, f.beta,
+                                                    R.act.data_ptr(), F, st))
+        else:
+            self._mm(R.xa, W, w + "mlp.gate_up", 2 * F, R.P, n)
+            _lib.check(lib.prl_glu_clamped(P, 2 * F, n, F, f.limit, f.beta, R.act.data_ptr(), f32, st))
+        return self._mm(R.act, F, w + "mlp.down", W, R.y0, n, split=True)
+
+    def _routed_ff(self, R, n, w, e, beta) -> torch.Tensor:
+        """Routed experts on xa: fp32 router logits, top-k with sigmoid weights, pairs grouped by expert on the device,
+        two grouped GEMMs around the gated activation.  Returns [top][n][W] fp32 (R.moe_out), to be summed by the caller."""
+        lib, st, W, f32 = self.lib, self._st, self.cfg.width, int(self.f32)
+        pairs = n * e.top
+        _lib.check(lib.prl_gemm_any(R.xa.data_ptr(), f32, W, self.arena.ptr(w + "mlp.router"), f32, W, n, e.experts, W,
+                                    R.router.data_ptr(), e.experts, st))
+        _lib.check(lib.prl_moe_route(R.router.data_ptr(), e.experts, n, e.experts, e.top, 0, R.sel.data_ptr(),
+                                     R.wsel.data_ptr(), R.perm.data_ptr(), R.moe_meta.data_ptr(), R.moe_tiles.data_ptr(), st))
+        tiles = int(lib.prl_moe_max_tiles(pairs, e.experts))
+        table = (R.perm.data_ptr(), R.moe_meta.data_ptr(), R.moe_tiles.data_ptr(), tiles)
+        _lib.check(lib.prl_moe_gemm(R.xa.data_ptr(), f32, W, n, self.arena.ptr(w + "mlp.experts.gate_up"), f32,
+                                    2 * e.ff * W, W, *table, 2 * e.ff, W, R.P.data_ptr(), 2 * e.ff, 0, st))
+        _lib.check(lib.prl_moe_glu(R.P.data_ptr(), 2 * e.ff, pairs, e.ff, R.perm.data_ptr(), R.wsel.data_ptr(), e.limit, beta,
+                                   R.moe_act.data_ptr(), f32, st))
+        _lib.check(lib.prl_moe_gemm(R.moe_act.data_ptr(), f32, e.ff, 0, self.arena.ptr(w + "mlp.experts.down"), f32,
+                                    W * e.ff, e.ff, *table, W, e.ff, R.moe_out.data_ptr(), W, 1, st))
+        return R.moe_out
+
+    def _mlstm_mixer(self, R, n, i, L, w, segs, pieces) -> None:
+        """Matrix-memory LSTM: one projection [q | k | v | g | i | f]; the gates' running maximum is walked first (fp32),
+        which turns the cell into S <- keep S + take k v^T, the recurrence prl_decay_scan runs; the normaliser rides along
+        as one more value column (v with a one appended)."""
+        c, lib, st, vec, f32, W = L.mlstm, self.lib, self._st, self.vec, int(self.f32), self.cfg.width
+        H, nq, nv = c.heads, c.heads * c.dim, c.heads * c.vdim
+        ld, P = 2 * nq + 2 * nv + 2 * H, R.P.data_ptr()
+        seg_start, seg_len, seg_slot, ns = segs
+        self._mm(R.xa, W, w + "mix.in", ld, R.P, n)
+        gb = vec[w + "mix.gate.b"].data_ptr()
+        _lib.check(lib.prl_mlstm_gates(P, ld, 2 * nq + 2 * nv, 2 * nq + 2 * nv + H, gb, gb + 4 * H, c.gate_cap, H, seg_start,
+                                       seg_len, seg_slot, ns, self.mlstm_m[i].data_ptr(), R.gates.data_ptr(),
+                                       R.minv.data_ptr(), st))
+        _lib.check(lib.prl_append_one(P, ld, 2 * nq, n, H, c.vdim, R.aux.data_ptr(), st))
+        dv = c.vdim + 1
+        head = (P, ld, 0, nq, c.dim ** -0.5, R.aux.data_ptr(), H * dv, 0, R.gates.data_ptr(), 2 * H, 0, None, H, c.dim, dv)
+        if pieces is not None:
+            _lib.check(lib.prl_decay_scan_split(*head, seg_slot, ns, *pieces, self.mlstm_state[i].data_ptr(), R.o.data_ptr(),
+                                                H * dv, st))
+        else:
+            _lib.check(lib.prl_decay_scan(*head, seg_start, seg_len, seg_slot, ns, self.mlstm_state[i].data_ptr(),
+                                          R.o.data_ptr(), H * dv, st))
+        _lib.check(lib.prl_mlstm_out(R.o.data_ptr(), n, H, c.vdim, R.minv.data_ptr(), c.den_eps, P + 4 * (2 * nq + nv), ld,
+                                     vec[w + "mix.norm"].data_ptr(), self.cfg.eps, R.ya.data_ptr(), f32, st))
+        k0 = self._mm(R.ya, nv, w + "mix.o", W, R.y0, n, split=True)
+        self._close(R, n, R.y0, k0, post_gain=vec[w + "norm1b"] if L.sandwich else vec[w + "norm1"],
+                    next_gain=self._next_gain(i, True))
+
+    def _attn_lightning_mixer(self, R, n, i, L, w, segs, pieces, max_q, row_pos, seg_pos0) -> None:
+        """Softmax attention (values = keys, per-head unit norms, capped scores, window + kept first tokens) beside
+        lightning attention, both from ONE projection [q | k || q | k | v | g]; each branch is normed over the width
+        with its own gain before the two are averaged."""
+        a, r, lib, st, vec, f32, W = L.attn, L.lin, self.lib, self._st, self.vec, int(self.f32), self.cfg.width
+        eps = self.cfg.eps
+        nq, nk, no = a.heads * a.dim, a.kv_heads * a.dim, a.heads * a.vdim
+        rq, rv = r.heads * r.dim, r.heads * r.vdim
+        ld, P = nq + nk + 2 * rq + 2 * rv, R.P.data_ptr()
+        seg_start, seg_len, seg_slot, ns = segs
+        self._mm(R.xa, W, w + "mix.in", ld, R.P, n)
+        # -- left
+        qb = vec[w + "mix.left.b"].data_ptr()
+        _lib.check(lib.prl_qk_headnorm_cache(P, ld, 0, nq, -1, n, a.heads, a.kv_heads, a.dim, a.vdim, qb, qb + 4 * nq, None,
+                                             None, eps, row_pos.data_ptr(), R.row_slot.data_ptr(),
+                                             self.block_table.data_ptr(), self.max_blocks, PAGE_SIZE, R.q.data_ptr(),
+                                             self.k_pool[i].data_ptr(), self.v_pool[i].data_ptr(), f32, st))
+        _lib.check(lib.prl_attn_any_masked(R.q.data_ptr(), self.k_pool[i].data_ptr(), self.v_pool[i].data_ptr(), f32,
+                                           self.block_table.data_ptr(), self.max_blocks, PAGE_SIZE, seg_start, seg_len,
+                                           seg_pos0.data_ptr(), seg_slot, ns, max_q, a.heads, a.kv_heads, a.dim, a.vdim,
+                                           a.scale, a.window, a.keep_first, a.softcap, 1, R.ya.data_ptr(), st))
+        k0 = self._mm(R.ya, no, w + "mix.left.o", W, R.y0, n, split=True)
+        # -- right
+        off = nq + nk
+        _lib.check(lib.prl_act_cols(P, ld, off, n, 2 * rq + rv, 0, st))            # SiLU on q, k, v
+        head = (P, ld, off, off + rq, 1.0, P, ld, off + 2 * rq, None, 0, 0, self.lin_decay[i].data_ptr(), r.heads, r.dim, r.vdim)
+        if pieces is not None:
+            _lib.check(lib.prl_decay_scan_split(*head, seg_slot, ns, *pieces, self.lin_state[i].data_ptr(), R.o2.data_ptr(),
+                                                rv, st))
+        else:
+            _lib.check(lib.prl_decay_scan(*head, seg_start, seg_len, seg_slot, ns, self.lin_state[i].data_ptr(),
+                                          R.o2.data_ptr(), rv, st))
+        _lib.check(lib.prl_gate_norm(R.o2.data_ptr(), 1, rv, P + 4 * (off + 2 * rq + rv), ld, vec[w + "mix.right.norm"].data_ptr(),
+                                     rv, rv, n, rv, 1, 0, 1, eps, R.yb.data_ptr(), f32, st))
+        k1 = self._mm(R.yb, rv, w + "mix.right.o", W, R.y1, n, split=True)
+        self._close(R, n, R.y0, k0, gain0=vec[w + "mix.left.out"], s0=L.left_scale, y1=R.y1, k1=k1,
+                    gain1=vec[w + "mix.right.out"], s1=L.right_scale,
+                    post_gain=vec[w + "norm1b"] if L.sandwich else vec[w + "norm1"], next_gain=self._next_gain(i, True))
+
+    def _embed(self, R, n, tokens, positions) -> None:
+        cfg, lib, st = self.cfg, self.lib, self._st
+        if cfg.positions == "sinusoid":
+            x0a = R.x0a.data_ptr() if cfg.loop_times else None
+            _lib.check(lib.prl_embed_sinusoid(tokens.data_ptr(), self.arena.ptr("embed"), int(self.f32), cfg.embed_scale,
+                                              self.pos_freq.data_ptr(), positions.data_ptr(), n, cfg.width, cfg.vocab_size,
+                                              R.x.data_ptr(), R.xa.data_ptr(), x0a, st))
+        else:
+            _lib.check(lib.prl_embed_scale(tokens.data_ptr(), self.arena.ptr("embed"), int(self.f32), cfg.embed_scale, n,
+                                           cfg.width, cfg.vocab_size, R.x.data_ptr(), R.xa.data_ptr(), st))
 
     # ---- one token for every slot (captured into the engine's CUDA graph) ---------------------------------------------
     def _step_kernels(self) -> None:
         cfg, lib, R, B = self.cfg, self.lib, self._dec, self.B
         self._st = st = _lib.stream_ptr()
         _lib.check(lib.prl_decode_rows(self.active.data_ptr(), B, R.seg[1].data_ptr(), R.row_slot.data_ptr(), st))
-        _lib.check(lib.prl_embed_scale(self.tokens.data_ptr(), self.arena.ptr("embed"), int(self.f32), cfg.embed_scale, B,
-                                       cfg.width, cfg.vocab_size, R.x.data_ptr(), R.xa.data_ptr(), st))
+        self._embed(R, B, self.tokens, self.positions)
         self._layers(R, B, B, 1, self.positions, self.positions, decode=True)
         _lib.check(lib.prl_rmsnorm_rows(R.x.data_ptr(), None, self.vec["final.norm"].data_ptr(), cfg.eps, B, cfg.width,
                                         R.xa.data_ptr(), int(self.f32), st))
@@ -582,8 +997,7 @@ class HybridEngine(EngineCore):
         R.row_back[:n].copy_(torch.tensor(back, dtype=i32), non_blocking=True)
         R.seg[:, :ns].copy_(torch.tensor(meta, dtype=i32), non_blocking=True)
         self._st = st = _lib.stream_ptr()
-        _lib.check(lib.prl_embed_scale(R.tokens.data_ptr(), self.arena.ptr("embed"), int(self.f32), cfg.embed_scale, n,
-                                       cfg.width, cfg.vocab_size, R.x.data_ptr(), R.xa.data_ptr(), st))
+        self._embed(R, n, R.tokens, R.row_pos)
         self._layers(R, n, ns, max(k for _, _, k in segs), R.row_pos, R.seg[2], trace=trace)
         self.stats["prefill_tokens"] += n
         if not want_rows:

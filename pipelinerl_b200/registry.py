@@ -103,6 +103,11 @@ def _povurax_config(config: dict, shapes: dict):
     return HybridConfig.from_povurax(config, shapes)
 
 
+def _belelorn_config(config: dict, shapes: dict):
+    from .hybrid import HybridConfig
+    return HybridConfig.from_belelorn(config, shapes)
+
+
 def _hybrid_engine():
     from .hybrid import HybridEngine
     return HybridEngine
@@ -110,6 +115,7 @@ def _hybrid_engine():
 
 register(Family("Qwen2ForCausalLM", _qwen2_config, _qwen2_engine, (torch.bfloat16,)))
 register(Family("Povurax", _povurax_config, _hybrid_engine, (torch.bfloat16, torch.float32)))
+register(Family("Belelorn", _belelorn_config, _hybrid_engine, (torch.bfloat16, torch.float32)))
 
 
 def parse_dtype(name: str) -> torch.dtype:
