@@ -94,13 +94,13 @@ def windowed_attention(h, wt, p, a, eps, round_in=None):
     qn, kn = rms_unit(q, eps), rms_unit(kv, eps)
     out = torch.zeros(T, H, d, dtype=F64)
     for t in range(T):
-        seen = [j for j in range(t + 1) if t - j < win or j < first]
+        seen = torch.tensor([j for j in range(t + 1) if t - j < win or j < first])
         for head in range(H):
             g = head // (H // G)
-            s = torch.stack([kn[j, g] @ qn[t, head] for j in seen]) * a["scale"]
-            s = a["softcap"] * torch.tanh(s / a["softcap"])
-            w = torch.softmax(s, dim=0)
-            out[t, head] = sum(w[n] * kv[j, g] for n, j in enumerate(seen))
+            s = (kn[seen, g] @ qn[t, head]) * a["scale"]
+            if a.get("softcap"):
+                s = a["softcap"] * torch.tanh(s / a["softcap"])
+            out[t, head] = torch.softmax(s, dim=0) @ kv[seen, g]
     return _mm(out.reshape(T, H * d), wt[p + "o"], round_in)
 
 
@@ -139,14 +139,19 @@ def clamped_expert(h, wt, p, limit, round_in=None):
     return _mm(g * torch.sigmoid(1.702 * g) * (u + 1.0), wt[p + "down"], round_in)
 
 
-def routed_ff(h, wt, p, mlp, round_in=None):
+def routed_ff(h, wt, p, mlp, round_in=None, margins=None):
     """Sigmoid router; each token's `top` best experts get the token SCALED by their score (scores not renormalised);
-    a shared expert sees every token unscaled."""
+    a shared expert sees every token unscaled.  `margins` (a list) receives, per token, the gap between the router
+    logits of the last expert taken and the first one left out."""
     T, W = h.shape
-    score = torch.sigmoid(_mm(h, wt[p + "router"], round_in))
+    logit = _mm(h, wt[p + "router"], round_in)
+    score = torch.sigmoid(logit)
     out = torch.zeros(T, W, dtype=F64)
+    n_exp, top = mlp["router"]["experts"], mlp["router"]["top"]
     for t in range(T):
-        order = sorted(range(mlp["router"]["experts"]), key=lambda e: -float(score[t, e]))
+        order = sorted(range(n_exp), key=lambda e: -float(score[t, e]))
+        if margins is not None:
+            margins.append(float(logit[t, order[top - 1]] - logit[t, order[top]]) if top < n_exp else math.inf)
         for e in order[:mlp["router"]["top"]]:
             out[t] += clamped_expert((score[t, e] * h[t])[None], wt, f"{p}e{e}.", mlp["expert"]["limit"], round_in)[0]
     if mlp.get("shared") is not None:
@@ -168,8 +173,9 @@ def layer_runs(cfg):
     return runs + [(i, None) for i in range(b, n)]
 
 
-def forward(cfg, wt, tokens, residuals=None, round_in=None):
-    """Logits [T, vocab] of a whole sequence; `residuals` collects the stream after every layer run."""
+def forward(cfg, wt, tokens, residuals=None, round_in=None, margins=None):
+    """Logits [T, vocab] of a whole sequence; `residuals` collects the stream after every layer run, `margins` the
+    router margins of every routed feed-forward run (one list of T gaps per run)."""
     eps = cfg["norm"]["eps"]
     x0 = embed(tokens, wt)
     x = x0
@@ -190,7 +196,10 @@ def forward(cfg, wt, tokens, residuals=None, round_in=None):
             if L["mlp"]["kind"] == "dense":
                 y = relu2_ff(hin, wt, p + "mlp.", round_in)
             else:
-                y = routed_ff(hin, wt, p + "mlp.", L["mlp"], round_in)
+                gaps = [] if margins is not None else None
+                y = routed_ff(hin, wt, p + "mlp.", L["mlp"], round_in, gaps)
+                if margins is not None:
+                    margins.append(gaps)
             x = x + norm_zero_centred(y, wt[p + "norm2b"], eps)
         if residuals is not None:
             residuals.append(x.clone())
