@@ -57,10 +57,12 @@ def parse():
     ap.add_argument("--no-rollout", action="store_true", help="N = 1: skip the full-rollout run through the plugin API")
     ap.add_argument("--rollout-tokens", type=int, default=8192, help="max_tokens of the full-rollout component")
     ap.add_argument("--splits", default="", help="learner counts of the split runs, e.g. '2,4' (default: by N)")
-    ap.add_argument("--arch", default="qwen2", choices=["qwen2", "hybrid"],
+    ap.add_argument("--arch", default="qwen2", choices=["qwen2", "hybrid", "belelorn"],
                     help="hybrid: prefill / decode throughput of the hybrid decoder family (GLA, attention + state-space "
                          "layers) beside the Qwen2 engine at equal sizes, and its kernels against their rooflines "
-                         "(tools/hybrid_bench.py); the default workload and its JSON contract are unchanged")
+                         "(tools/hybrid_bench.py); belelorn: the same for the Belelorn design (mLSTM, windowed attention "
+                         "beside lightning attention, routed feed-forwards) beside the Povurax hybrid and Qwen2; the default "
+                         "workload and its JSON contract are unchanged")
     ap.add_argument("--sizes", default="w2048,w4096", help="--arch hybrid: model sizes to compare")
     return ap.parse_args()
 
@@ -616,20 +618,22 @@ def run_hybrid(args):
     sampler = ClockSampler(0)
     sampler.start()
     sizes = args.sizes.split(",")
-    res = hybrid_bench.run(sizes, prompt=4096, context=2048, batch=32, steps=args.steps, warm=max(3, args.warmup))
+    which = "belelorn" if args.arch == "belelorn" else "hybrid"
+    runner = hybrid_bench.run_belelorn if which == "belelorn" else hybrid_bench.run
+    res = runner(sizes, prompt=4096, context=2048, batch=32, steps=args.steps, warm=max(3, args.warmup))
     clocks = sampler.stop()
-    first = res[sizes[0]]["hybrid"]
-    print(json.dumps({"metric": "hybrid_decode_tokens_per_s", "value": first["decode_tokens_per_s"], "unit": UNIT, "n_gpus": 1,
+    first = res[sizes[0]][which]
+    print(json.dumps({"metric": f"{which}_decode_tokens_per_s", "value": first["decode_tokens_per_s"], "unit": UNIT, "n_gpus": 1,
                       "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": first["decode_ms_per_step"],
                       "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                      "config": {"model": f"hybrid {sizes[0]} (random init)", "global_batch": 32, "seq_len": 2048,
+                      "config": {"model": f"{which} {sizes[0]} (random init)", "global_batch": 32, "seq_len": 2048,
                                  "parallelism": "1 GPU", "l2": "inputs_exceed_l2 (weights + KV / states per step)"},
                       "clocks": clocks, "gpu_launches": _lib.launch_count() - before, "sizes": res}), flush=True)
 
 
 if __name__ == "__main__":
     a = parse()
-    if a.arch == "hybrid":
+    if a.arch in ("hybrid", "belelorn"):
         run_hybrid(a)
     elif a.impl == "reference":
         run_reference(a)

@@ -11,8 +11,11 @@
 //   4. gated activation of an expert with the pair's weight folded in: the weight multiplies the expert's INPUT, and
 //              the two first projections are linear, so gate and up are scaled after the product (in fp32).
 //
-// The GEMM is the CUDA-core kernel of gemm_any.cu with a row indirection: every output element is summed by one thread
-// in ascending k, so a token's result does not depend on which rows share its tile.
+// Two GEMM kernels walk the same tile table.  fp32 operands (and sizes a 16-byte copy cannot express) take the
+// CUDA-core kernel of gemm_any.cu with a row indirection: every output element is summed by one thread in ascending k.
+// bf16 operands take a tensor-core kernel (mma.sync m16n8k16, fp32 accumulators): 64 x 128 output tile per CTA of eight
+// warps, operands staged by cp.async (zero-filled past the edges) into a double buffer and read with ldmatrix.  A
+// row's result depends only on the row and the expert's weights, never on which rows share its tile.
 #include "prl_common.cuh"
 
 namespace prl {
@@ -172,6 +175,110 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const TA* __restrict__ A,
   }
 }
 
+// ---- bf16 tensor-core variant ------------------------------------------------------------------------------------------
+constexpr int kBN = 128, kBK = 32, kPad = 8;      // tile N, K step, padding (halves) that keeps ldmatrix conflict-free
+constexpr int kLds = kBK + kPad;                  // 40 halves = 80 bytes per staged row
+
+__device__ __forceinline__ void cp_async16_zfill(void* dst, const void* src, int bytes) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(256) moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, int a_mod,
+                                                           const __nv_bfloat16* __restrict__ W, int64_t expert_stride,
+                                                           int64_t ldw, const int32_t* __restrict__ perm,
+                                                           const int32_t* __restrict__ meta, const int32_t* __restrict__ tiles,
+                                                           int N, int K, float* __restrict__ C, int64_t ldc, int c_perm) {
+  pdl_wait();
+  const int tile = blockIdx.y;
+  if (tile >= meta[0]) return;
+  __shared__ __align__(16) __nv_bfloat16 As[2][kTile][kLds];
+  __shared__ __align__(16) __nv_bfloat16 Bs[2][kBN][kLds];
+  __shared__ int32_t a_row[kTile], c_row[kTile];
+  const int e = tiles[3 * tile], s0 = tiles[3 * tile + 1], M = tiles[3 * tile + 2];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid < kTile) {
+    const int s = s0 + min(tid, M - 1);
+    const int p = perm[s];
+    a_row[tid] = a_mod > 0 ? p % a_mod : s;
+    c_row[tid] = c_perm ? p : s;
+  }
+  __syncthreads();
+  const __nv_bfloat16* We = W + (int64_t)e * expert_stride;
+  const int n0 = blockIdx.x * kBN;
+  const int wm = (warp >> 2) * 32, wn = (warp & 3) * 32;       // warp tile 32 x 32
+  float acc[2][4][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) acc[i][j][q] = 0.f;
+  // loaders: A 64 rows x 4 chunks of 8 halves (one per thread), B 128 rows x 4 chunks (two per thread)
+  const int lr = tid >> 2, lc = (tid & 3) * 8;
+  const int64_t a_off = (int64_t)a_row[lr] * lda;
+  auto stage = [&](int k0, int buf) {
+    const int k = k0 + lc;
+    const bool kin = k < K;
+    cp_async16_zfill(&As[buf][lr][lc], A + a_off + (kin ? k : 0), (kin && lr < M) ? 16 : 0);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = lr + 64 * h, nn = n0 + r;
+      const bool ok = kin && nn < N;
+      cp_async16_zfill(&Bs[buf][r][lc], We + (int64_t)(ok ? nn : 0) * ldw + (kin ? k : 0), ok ? 16 : 0);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  stage(0, 0);
+  int buf = 0;
+  for (int k0 = 0; k0 < K; k0 += kBK, buf ^= 1) {
+    if (k0 + kBK < K) {
+      stage(k0 + kBK, buf ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < kBK; kk += 16) {
+      uint32_t af[2][4], bf[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) ldsm_x4(af[i], &As[buf][wm + 16 * i + (lane & 15)][kk + (lane >> 4) * 8]);
+#pragma unroll
+      for (int j = 0; j < 2; ++j) ldsm_x4(bf[j], &Bs[buf][wn + 16 * j + (lane & 7) + ((lane >> 4) << 3)][kk + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) mma_bf16(acc[i][j], af[i], bf[j >> 1][(j & 1) * 2], bf[j >> 1][(j & 1) * 2 + 1]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int m = wm + 16 * i + (lane >> 2) + 8 * half;
+      if (m >= M) continue;
+      float* crow = C + (int64_t)c_row[m] * ldc;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int nn = n0 + wn + 8 * j + (lane & 3) * 2;
+        if (nn < N) crow[nn] = acc[i][j][2 * half];
+        if (nn + 1 < N) crow[nn + 1] = acc[i][j][2 * half + 1];
+      }
+    }
+}
+
 // act[s] = g * sigmoid(beta g) * (u + 1),  g = min(w * gate, lim), u = clamp(w * up, -lim, lim),  w = wsel[perm[s]]
 template <typename T>
 __global__ void moe_glu_kernel(const float* __restrict__ gu, int64_t ld, int F, const int32_t* __restrict__ perm,
@@ -215,8 +322,16 @@ extern "C" int prl_moe_gemm(const void* A, int32_t a_is_f32, int64_t lda, int32_
   PRL_CHECK_ARG(A && W && perm && meta && tiles && C, "prl_moe_gemm: NULL argument");
   PRL_CHECK_ARG(max_tiles >= 1 && max_tiles <= 65535 && N >= 1 && K >= 1 && lda >= K && ldw >= K && ldc >= N && a_mod >= 0,
                 "prl_moe_gemm: bad shape (tiles=%lld N=%lld K=%lld)", (long long)max_tiles, (long long)N, (long long)K);
-  dim3 grid((unsigned)((N + kTile - 1) / kTile), (unsigned)max_tiles);
   cudaStream_t s = (cudaStream_t)st;
+  if (!a_is_f32 && !w_is_f32 && K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 && expert_stride % 8 == 0 &&
+      ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0) {
+    dim3 grid_tc((unsigned)((N + kBN - 1) / kBN), (unsigned)max_tiles);
+    PRL_CUDA(launch_pdl(moe_gemm_mma_kernel, grid_tc, dim3(256), (size_t)0, s, (const bf16*)A, lda, a_mod, (const bf16*)W,
+                        expert_stride, ldw, perm, meta, tiles, (int)N, (int)K, C, ldc, c_perm));
+    PRL_LAUNCH_CHECK();
+    return PRL_OK;
+  }
+  dim3 grid((unsigned)((N + kTile - 1) / kTile), (unsigned)max_tiles);
 #define PRL_MG(TA, TW) PRL_CUDA(launch_pdl((moe_gemm_kernel<TA, TW>), grid, dim3(256), (size_t)0, s, (const TA*)A, lda, a_mod, (const TW*)W, \
                                            expert_stride, ldw, perm, meta, tiles, (int)N, (int)K, C, ldc, c_perm))
   if (a_is_f32 && w_is_f32) PRL_MG(float, float);

@@ -44,6 +44,27 @@ def hybrid_config(s):
                 layers=[gla if i % 2 == 0 else par for i in range(s["layers"])])
 
 
+def belelorn_config(s):
+    """Six layers of which the first two run twice (eight layer runs, the depth of the models beside it): attention
+    (windowed, values = keys, head size 128) beside lightning attention alternating with matrix-memory LSTM layers,
+    squared-ReLU feed-forwards of the same ff alternating with routed ones of the same active width (two of sixteen
+    experts of ff / 4 each plus a shared expert of ff / 2)."""
+    W, ff = s["width"], s["ff"]
+    par = dict(type="parallel",
+               mixer=dict(left=dict(heads=s["heads"], kv_heads=s["kv"], dim=128, vdim=128, scale=128 ** -0.5, softcap=30.0,
+                                    mask=dict(size=1024, keep_first=4)),
+                          right=dict(heads=W // 128, dim=128, vdim=128,
+                                     decay=[1.0 - 2.0 ** -(3 + 6 * h / max(1, W // 128 - 1)) for h in range(W // 128)])))
+    cell = dict(type="mlstm", mixer=dict(heads=W // 256, dim=128, vdim=256, gate_cap=15.0))
+    dense = dict(kind="dense", ff=ff)
+    routed = dict(kind="moe", router=dict(experts=16, top=2), expert=dict(ff=ff // 4, limit=7.0), shared=dict(ff=ff // 2, limit=7.0))
+    layers = []
+    for i in range(s["layers"] - 2):
+        layers.append(dict(par if i % 2 == 0 else cell, mlp=dense if i % 2 == 0 else routed))
+    return dict(architecture="Belelorn", vocab=s["vocab"], width=W, norm=dict(eps=1e-5), logit_scale=1.0, layers=layers,
+                loop=dict(start=0, stop=2, times=2))
+
+
 def peaks():
     try:
         p = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
@@ -246,6 +267,222 @@ def kernel_table(eng, s, batch, chunk, timer):
     return out
 
 
+def kernel_table_belelorn(eng, s, batch, chunk, timer):
+    """The kernels the Belelorn layers add, alone, at the decode shape (`batch` one-token segments at position 2047) and
+    the prefill shape (one segment of `chunk` rows at the start of a sequence): memory-bound ones against the measured
+    copy bandwidth, the recurrences and the CUDA-core products also against the SMs' fp32 FMA rate."""
+    from pipelinerl_b200 import _lib
+    from pipelinerl_b200.cache import PAGE_SIZE
+    from pipelinerl_b200.hybrid import _Rows
+    lib, cfg = eng.lib, eng.cfg
+    hbm, _, how = peaks()
+    fma_tflops = 148 * 128 * 2 * 1.965e9 / 1e12
+    W = cfg.width
+    pi = next(i for i, L in enumerate(cfg.layers) if L.kind == "parallel_lin")
+    mi = next(i for i, L in enumerate(cfg.layers) if L.kind == "mlstm")
+    par, cell = cfg.layers[pi], cfg.layers[mi]
+    a, r, c = par.attn, par.lin, cell.mlstm
+    e = cell.mlp.moe
+    st = _lib.stream_ptr()
+    out = {}
+    i32 = dict(dtype=torch.int32, device=eng.dev)
+    ctx = 2047
+    pages_per = (ctx + PAGE_SIZE) // PAGE_SIZE
+    for b in range(batch):
+        eng.block_table[b, :pages_per].copy_(torch.arange(1 + b * pages_per, 1 + (b + 1) * pages_per, **i32))
+    for shape, n, ns in (("decode", batch, batch), ("prefill", chunk, 1)):
+        R = _Rows(eng, n, pieces=shape == "prefill")
+        R.P.normal_(0, 0.5)
+        if shape == "decode":
+            R.seg.copy_(torch.stack([torch.arange(n, **i32), torch.ones(n, **i32), torch.full((n,), ctx, **i32), torch.arange(n, **i32)]))
+            R.row_slot.copy_(torch.arange(n, **i32)); R.row_pos.fill_(ctx)
+        else:
+            R.seg[:, :1].copy_(torch.tensor([[0], [n], [0], [0]], **i32))
+            R.row_slot.zero_(); R.row_pos.copy_(torch.arange(n, **i32))
+            step = eng.piece_tokens
+            n_sub = (n + step - 1) // step
+            R.sub[0, :n_sub].copy_(torch.arange(0, n, step, **i32))
+            R.sub[1, :n_sub].copy_(torch.tensor([min(step, n - k) for k in range(0, n, step)], **i32))
+            R.seg_sub[:, :1].copy_(torch.tensor([[0], [n_sub]], **i32))
+            pieces = (R.seg_sub[0].data_ptr(), R.seg_sub[1].data_ptr(), R.sub[0].data_ptr(), R.sub[1].data_ptr(), n_sub,
+                      R.scratch.data_ptr(), R.cdec.data_ptr())
+        seg = [R.seg[k].data_ptr() for k in range(4)]
+        vec = eng.vec
+        max_q = 1 if shape == "decode" else n
+        # -- attention: front end and the windowed kernel
+        nq, nk = a.heads * a.dim, a.kv_heads * a.dim
+        rq, rv = r.heads * r.dim, r.heads * r.vdim
+        ld = nq + nk + 2 * rq + 2 * rv
+        wp = f"l{par.weights_of}."
+        qb = vec[wp + "mix.left.b"].data_ptr()
+
+        def front():
+            _lib.check(lib.prl_qk_headnorm_cache(R.P.data_ptr(), ld, 0, nq, -1, n, a.heads, a.kv_heads, a.dim, a.vdim, qb, qb + 4 * nq,
+                                                 None, None, cfg.eps, R.row_pos.data_ptr(), R.row_slot.data_ptr(),
+                                                 eng.block_table.data_ptr(), eng.max_blocks, PAGE_SIZE, R.q.data_ptr(),
+                                                 eng.k_pool[pi].data_ptr(), eng.v_pool[pi].data_ptr(), 0, st))
+        ms = timer.events(front)
+        out[f"qk_headnorm_cache/{shape}"] = dict(ms=round(ms, 4), hbm_frac=round(n * ((nq + nk) * 4 + (nq + 2 * nk) * 2) / ms / 1e6 / hbm, 3))
+
+        def attn():
+            _lib.check(lib.prl_attn_any_masked(R.q.data_ptr(), eng.k_pool[pi].data_ptr(), eng.v_pool[pi].data_ptr(), 0,
+                                               eng.block_table.data_ptr(), eng.max_blocks, PAGE_SIZE, seg[0], seg[1], seg[2], seg[3],
+                                               ns, max_q, a.heads, a.kv_heads, a.dim, a.vdim, a.scale, a.window, a.keep_first,
+                                               a.softcap, 1, R.ya.data_ptr(), st))
+        ms = timer.events(attn)
+        keys = (min(ctx + 1, a.window + a.keep_first) * n) if shape == "decode" else sum(min(t + 1, a.window + a.keep_first) for t in range(n))
+        flops = 4.0 * keys * a.heads * a.dim
+        kv_b = (ns * min(ctx + 1, a.window + a.keep_first) if shape == "decode" else n) * a.kv_heads * a.dim * 2 * 2
+        out[f"attn_window/{shape}"] = dict(ms=round(ms, 4), hbm_frac=round((kv_b + n * nq * 4) / ms / 1e6 / hbm, 3),
+                                           fp32_fma_frac=round(flops / ms / 1e9 / fma_tflops, 3), tflops=round(flops / ms / 1e9, 2))
+        # -- lightning attention
+        off = nq + nk
+        head = (R.P.data_ptr(), ld, off, off + rq, 1.0, R.P.data_ptr(), ld, off + 2 * rq, None, 0, 0, eng.lin_decay[pi].data_ptr(),
+                r.heads, r.dim, r.vdim)
+
+        def silu():
+            _lib.check(lib.prl_act_cols(R.P.data_ptr(), ld, off, n, 2 * rq + rv, 0, st))
+        ms = timer.events(silu)
+        out[f"act_cols/{shape}"] = dict(ms=round(ms, 4), hbm_frac=round(n * (2 * rq + rv) * 8 / ms / 1e6 / hbm, 3))
+
+        def lin():
+            _lib.check(lib.prl_decay_scan(*head, seg[0], seg[1], seg[3], ns, eng.lin_state[pi].data_ptr(), R.o2.data_ptr(), rv, st))
+        ms = timer.events(lin)
+        state_b, io_b = 2 * ns * r.heads * r.dim * r.vdim * 4, n * (2 * rq + 2 * rv) * 4
+        flops = 5.0 * n * r.heads * r.dim * r.vdim
+        out[f"lightning_scan/{shape}"] = dict(ms=round(ms, 4), hbm_frac=round((state_b + io_b) / ms / 1e6 / hbm, 3),
+                                              fp32_fma_frac=round(flops / ms / 1e9 / fma_tflops, 3))
+        if shape == "prefill":
+            def lin_split():
+                _lib.check(lib.prl_decay_scan_split(*head, seg[3], ns, *pieces, eng.lin_state[pi].data_ptr(), R.o2.data_ptr(), rv, st))
+            ms = timer.events(lin_split)
+            out["lightning_scan_split/prefill"] = dict(ms=round(ms, 4), fp32_fma_frac=round(1.4 * flops / ms / 1e9 / fma_tflops, 3))
+        # -- matrix-memory LSTM
+        H, mq, mv = c.heads, c.heads * c.dim, c.heads * c.vdim
+        ldm = 2 * mq + 2 * mv + 2 * H
+        wm = f"l{cell.weights_of}."
+        gb = vec[wm + "mix.gate.b"].data_ptr()
+
+        def gates():
+            _lib.check(lib.prl_mlstm_gates(R.P.data_ptr(), ldm, 2 * mq + 2 * mv, 2 * mq + 2 * mv + H, gb, gb + 4 * H, c.gate_cap, H,
+                                           seg[0], seg[1], seg[3], ns, eng.mlstm_m[mi].data_ptr(), R.gates.data_ptr(),
+                                           R.minv.data_ptr(), st))
+        out[f"mlstm_gates/{shape}"] = dict(ms=round(timer.events(gates), 4))
+
+        def one():
+            _lib.check(lib.prl_append_one(R.P.data_ptr(), ldm, 2 * mq, n, H, c.vdim, R.aux.data_ptr(), st))
+        ms = timer.events(one)
+        out[f"append_one/{shape}"] = dict(ms=round(ms, 4), hbm_frac=round(n * mv * 8 / ms / 1e6 / hbm, 3))
+        dv = c.vdim + 1
+        mhead = (R.P.data_ptr(), ldm, 0, mq, c.dim ** -0.5, R.aux.data_ptr(), H * dv, 0, R.gates.data_ptr(), 2 * H, 0, None, H, c.dim, dv)
+
+        def cellscan():
+            _lib.check(lib.prl_decay_scan(*mhead, seg[0], seg[1], seg[3], ns, eng.mlstm_state[mi].data_ptr(), R.o.data_ptr(), H * dv, st))
+        ms = timer.events(cellscan)
+        state_b, io_b = 2 * ns * H * c.dim * dv * 4, n * (2 * mq + 2 * H * dv) * 4
+        flops = 5.0 * n * H * c.dim * dv
+        out[f"mlstm_scan/{shape}"] = dict(ms=round(ms, 4), hbm_frac=round((state_b + io_b) / ms / 1e6 / hbm, 3),
+                                          fp32_fma_frac=round(flops / ms / 1e9 / fma_tflops, 3))
+        if shape == "prefill":
+            def cell_split():
+                _lib.check(lib.prl_decay_scan_split(*mhead, seg[3], ns, *pieces, eng.mlstm_state[mi].data_ptr(), R.o.data_ptr(), H * dv, st))
+            ms = timer.events(cell_split)
+            out["mlstm_scan_split/prefill"] = dict(ms=round(ms, 4), fp32_fma_frac=round(1.4 * flops / ms / 1e9 / fma_tflops, 3))
+
+        def cellout():
+            _lib.check(lib.prl_mlstm_out(R.o.data_ptr(), n, H, c.vdim, R.minv.data_ptr(), c.den_eps, R.P.data_ptr() + 4 * (2 * mq + mv),
+                                         ldm, vec[wm + "mix.norm"].data_ptr(), cfg.eps, R.ya.data_ptr(), 0, st))
+        ms = timer.events(cellout)
+        out[f"mlstm_out/{shape}"] = dict(ms=round(ms, 4), hbm_frac=round(n * mv * (4 + 4 + 2) / ms / 1e6 / hbm, 3))
+        # -- the closing kernel with both branches (the Qwen2 engine's residual + norm kernel is its counterpart)
+        def close():
+            eng._st = st
+            eng._close(R, n, R.y0, 1, gain0=vec[wp + "mix.left.out"], s0=0.5, y1=R.y1, k1=1, gain1=vec[wp + "mix.right.out"], s1=0.5,
+                       post_gain=vec[wp + "norm1b"], next_gain=vec[wp + "norm2"])
+        ms = timer.events(close)
+        out[f"sublayer_close/{shape}"] = dict(ms=round(ms, 4), hbm_frac=round(n * W * (4 * 4 + 2) / ms / 1e6 / hbm, 3))
+        # -- routed feed-forward
+        eng._st = st
+        R.xa.normal_(0, 1.0)
+
+        def routed():
+            eng._routed_ff(R, n, wm, e, cell.mlp.beta)
+        ms = timer.events(routed)
+        flops = 2.0 * n * e.top * 3 * e.ff * W
+        wbytes = min(e.experts, n * e.top) * 3 * e.ff * W * 2
+        out[f"routed_ff/{shape}"] = dict(ms=round(ms, 4), hbm_frac=round(wbytes / ms / 1e6 / hbm, 3), tflops=round(flops / ms / 1e9, 2),
+                                         fp32_fma_frac=round(flops / ms / 1e9 / fma_tflops, 3))
+        F = par.mlp.ff
+
+        def relu2():
+            _lib.check(lib.prl_act_store(R.P.data_ptr(), F, n, F, 0, R.act.data_ptr(), 0, st))
+        ms = timer.events(relu2)
+        out[f"relu2/{shape}"] = dict(ms=round(ms, 4), hbm_frac=round(n * F * (4 + 2) / ms / 1e6 / hbm, 3))
+        h = torch.zeros(n, W, dtype=torch.float32, device=eng.dev)
+        xb = torch.zeros(n, W, dtype=torch.bfloat16, device=eng.dev)
+        gam = torch.ones(W, dtype=torch.bfloat16, device=eng.dev)
+        part = torch.randn(n, 2 * F, dtype=torch.float32, device=eng.dev)
+        actb = torch.zeros(n, F, dtype=torch.bfloat16, device=eng.dev)
+
+        def qres():
+            _lib.check(lib.prl_residual_rmsnorm(part.data_ptr(), 1, n, W, gam.data_ptr(), 1e-6, h.data_ptr(), xb.data_ptr(), None, 0, st))
+        ms = timer.events(qres)
+        out[f"qwen2.residual_rmsnorm/{shape}"] = dict(ms=round(ms, 4), hbm_frac=round(n * W * (3 * 4 + 2) / ms / 1e6 / hbm, 3))
+
+        def qsilu():
+            _lib.check(lib.prl_silu_mul(part.data_ptr(), 1, n, F, actb.data_ptr(), None, 0, st))
+        ms = timer.events(qsilu)
+        out[f"qwen2.silu_mul/{shape}"] = dict(ms=round(ms, 4), hbm_frac=round(n * F * (8 + 2) / ms / 1e6 / hbm, 3))
+        del R
+    eng.block_table.zero_()
+    out["_denominators"] = {"hbm_gbs": hbm, "hbm": how, "fp32_fma_tflops_nominal": round(fma_tflops, 1)}
+    return out
+
+
+def run_belelorn(sizes, prompt, context, batch, steps, warm, kernels=True, e2e=True, others=True):
+    """Belelorn beside the Povurax hybrid and the Qwen2 engine at equal width / depth / ff / attention heads."""
+    from pipelinerl_b200.engine import DecodeEngine
+    from pipelinerl_b200.hybrid import HybridConfig, HybridEngine
+    from pipelinerl_b200.model import ModelConfig, ParamArena
+    dev = torch.device("cuda:0")
+    timer = Timer()
+    res = {}
+    for name in sizes:
+        s = SIZES[name]
+        kw = dict(max_batch=batch, max_seq_len=max(prompt, context) + 256, max_new_tokens=warm + steps + 8, device=dev,
+                  prefill_chunk=1024)
+        entry = {}
+        if e2e and others:
+            qcfg = ModelConfig(vocab_size=s["vocab"], hidden_size=s["width"], intermediate_size=s["ff"], num_layers=s["layers"],
+                               num_q_heads=s["heads"], num_kv_heads=s["kv"])
+            eng = DecodeEngine(qcfg, ParamArena(qcfg, dev).init_random(seed=1), **kw)
+            entry["qwen2"] = end_to_end(eng, s["vocab"], prompt, context, batch, steps, warm)
+            entry["qwen2"]["params_M"] = round(qcfg.num_params() / 1e6)
+            del eng
+            torch.cuda.empty_cache()
+            hcfg = HybridConfig.from_povurax(hybrid_config(s))
+            eng = HybridEngine(hcfg, ParamArena(hcfg, dev).init_random(seed=1), **kw)
+            entry["povurax"] = end_to_end(eng, s["vocab"], prompt, context, batch, steps, warm)
+            entry["povurax"]["params_M"] = round(hcfg.num_params() / 1e6)
+            del eng
+            torch.cuda.empty_cache()
+        bcfg = HybridConfig.from_belelorn(belelorn_config(s))
+        eng = HybridEngine(bcfg, ParamArena(bcfg, dev).init_random(seed=1), **kw)
+        if e2e:
+            entry["belelorn"] = end_to_end(eng, s["vocab"], prompt, context, batch, steps, warm)
+            entry["belelorn"]["params_M"] = round(bcfg.num_params() / 1e6)
+            for other in ("qwen2", "povurax"):
+                if other in entry:
+                    entry[f"belelorn_over_{other}"] = {k: round(entry["belelorn"][f"{k}_tokens_per_s"] / entry[other][f"{k}_tokens_per_s"], 3)
+                                                       for k in ("prefill", "decode")}
+        if kernels:
+            entry["kernels"] = kernel_table_belelorn(eng, s, batch, 1024, timer)
+        res[name] = entry
+        del eng
+        torch.cuda.empty_cache()
+    return res
+
+
 def run(sizes, prompt, context, batch, steps, warm, kernels=True, e2e=True):
     from pipelinerl_b200.engine import DecodeEngine
     from pipelinerl_b200.hybrid import HybridConfig, HybridEngine
@@ -292,11 +529,17 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-kernels", action="store_true")
     ap.add_argument("--only-kernels", action="store_true", help="skip the end-to-end runs (a small case for a profiler)")
+    ap.add_argument("--design", default="povurax", choices=["povurax", "belelorn"], help="which hybrid design is measured")
+    ap.add_argument("--alone", action="store_true", help="--design belelorn: skip the Qwen2 and Povurax runs beside it")
     a = ap.parse_args()
     from pipelinerl_b200 import _lib
     before = _lib.launch_count()
-    res = run(a.sizes.split(","), a.prompt, a.context, a.batch, a.steps, a.warmup, kernels=not a.no_kernels, e2e=not a.only_kernels)
-    print(json.dumps({"bench": "hybrid_vs_qwen2", "dtype": "bf16", "data": "synthetic", "prompt": a.prompt,
+    if a.design == "belelorn":
+        res = run_belelorn(a.sizes.split(","), a.prompt, a.context, a.batch, a.steps, a.warmup, kernels=not a.no_kernels,
+                           e2e=not a.only_kernels, others=not a.alone)
+    else:
+        res = run(a.sizes.split(","), a.prompt, a.context, a.batch, a.steps, a.warmup, kernels=not a.no_kernels, e2e=not a.only_kernels)
+    print(json.dumps({"bench": f"{a.design}_vs_qwen2", "dtype": "bf16", "data": "synthetic", "prompt": a.prompt,
                       "context": a.context, "batch": a.batch, "steps": a.steps, "warmup": a.warmup,
                       "gpu_launches": _lib.launch_count() - before, "sizes": res}), flush=True)
 
