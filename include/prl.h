@@ -695,6 +695,9 @@ int prl_attn_any_masked(const void* q, const void* k_pool, const void* v_pool, i
                         const int32_t* seg_pos0, const int32_t* seg_slot, int32_t n_seg, int32_t max_q, int32_t H,
                         int32_t G, int32_t dim, int32_t vdim, float scale, int32_t window, int32_t keep_first,
                         float softcap, int32_t out_is_t, void* out, prl_stream_t stream);
+/* bf16 prompt portions with head sizes 32 / 64 / 128 (dim == vdim) take a tensor-core kernel inside prl_attn_any*;
+ * 0 switches it off process-wide (tests compare the two kernels) */
+void prl_attn_any_tensor_cores(int32_t on);
 /* in-place SiLU of columns off .. off + C of P (act = 0); out = T(relu(P)^2) (act = 0) */
 int prl_act_cols(float* P, int64_t ld, int32_t off, int32_t n, int32_t C, int32_t act, prl_stream_t stream);
 int prl_act_store(const float* P, int64_t ld, int32_t n, int32_t F, int32_t act, void* out, int32_t f32,

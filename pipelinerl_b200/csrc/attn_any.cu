@@ -20,6 +20,14 @@
 #include <math.h>
 
 namespace prl {
+
+// attn_mma.cu: the tensor-core kernel for prompt portions in bf16 with head sizes it is built for
+bool attn_mma_fits(int dim, int vdim, const void* q, const void* k_pool, const void* v_pool);
+int attn_mma_launch(const void* q, const void* kp, const void* vp, const int32_t* bt, int max_blocks, int page_size,
+                    const int32_t* ss, const int32_t* sl, const int32_t* sp, const int32_t* sslot, int n_seg, int max_q, int H,
+                    int G, int dim, float scale, int window, int keep_first, float softcap, int out_is_bf16, void* out,
+                    cudaStream_t st);
+
 namespace {
 
 constexpr int kWarpsPerCta = 8;
@@ -270,7 +278,22 @@ __global__ void __launch_bounds__(kDecWarps * 32) attn_decode_any_kernel(
     if (seen) {
       const T* kr = k_pool + (((int64_t)bt[kt / page_size] * G + g) * page_size + kt % page_size) * dim;
       if (vec) {
-        for (int d = 0; d < dim; d += E) {
+        int d = 0;
+        for (; d + 4 * E <= dim; d += 4 * E) {              // four 16-byte loads in flight per lane
+          uint4 raw[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) raw[u] = *reinterpret_cast<const uint4*>(kr + d + u * E);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            float kf[E];
+            unpack16<T>(raw[u], kf);
+#pragma unroll
+            for (int hh = 0; hh < kDecHeads; ++hh)
+#pragma unroll
+              for (int e = 0; e < E; ++e) dot[hh] = fmaf(Qs[hh * dim + d + u * E + e], kf[e], dot[hh]);
+          }
+        }
+        for (; d < dim; d += E) {
           float kf[E];
           unpack16<T>(*reinterpret_cast<const uint4*>(kr + d), kf);
 #pragma unroll
@@ -304,22 +327,28 @@ __global__ void __launch_bounds__(kDecWarps * 32) attn_decode_any_kernel(
       for (int i = 0; i < VR; ++i) acc[hh][i] *= corr;
     }
     const uint32_t seen_mask = __ballot_sync(0xffffffffu, seen);
-    for (int j = 0; j < kKeysPerTile; ++j) {
-      if (!(seen_mask >> j & 1u)) continue;                    // warp-uniform
-      const int kj = k0 + j;
-      const T* vr = v_pool + (((int64_t)bt[kj / page_size] * G + g) * page_size + kj % page_size) * vdim;
-      float vv[VR];
+    for (int j0 = 0; j0 < kKeysPerTile; j0 += 4) {             // the loads of four keys in flight together
+      if (!(seen_mask >> j0 & 0xfu)) continue;                 // warp-uniform
+      float vv[4][VR];
 #pragma unroll
-      for (int i = 0; i < VR; ++i) {
-        const int c = lane + 32 * i;
-        vv[i] = c < vdim ? cvt(vr[c]) : 0.f;
+      for (int u = 0; u < 4; ++u) {
+        const int kj = k0 + j0 + u;
+        const bool on = seen_mask >> (j0 + u) & 1u;            // hidden keys are not read: their weight is zero anyway
+        const T* vr = v_pool + (((int64_t)bt[(on ? kj : k0) / page_size] * G + g) * page_size + (on ? kj : k0) % page_size) * vdim;
+#pragma unroll
+        for (int i = 0; i < VR; ++i) {
+          const int c = lane + 32 * i;
+          vv[u][i] = (on && c < vdim) ? cvt(vr[c]) : 0.f;
+        }
       }
 #pragma unroll
-      for (int hh = 0; hh < kDecHeads; ++hh) {
-        const float pj = __shfl_sync(0xffffffffu, p[hh], j);
+      for (int u = 0; u < 4; ++u)
 #pragma unroll
-        for (int i = 0; i < VR; ++i) acc[hh][i] = fmaf(pj, vv[i], acc[hh][i]);
-      }
+        for (int hh = 0; hh < kDecHeads; ++hh) {
+          const float pj = __shfl_sync(0xffffffffu, p[hh], j0 + u);
+#pragma unroll
+          for (int i = 0; i < VR; ++i) acc[hh][i] = fmaf(pj, vv[u][i], acc[hh][i]);
+        }
     }
   }
 #pragma unroll
@@ -392,6 +421,12 @@ int dispatch_attn(int vr, const void* q, const void* kp, const void* vp, const i
 
 using namespace prl;
 
+constexpr int kMmaMinRows = 16;      // the longest segment of the batch has at least this many rows: tensor-core tiles pay
+static int g_attn_tensor_cores = 1;
+
+// Tests compare the tensor-core kernel with the CUDA-core one on the same cache: 0 switches the former off (process-wide).
+extern "C" void prl_attn_any_tensor_cores(int32_t on) { g_attn_tensor_cores = on ? 1 : 0; }
+
 static int attn_any_impl(const void* q, const void* k_pool, const void* v_pool, int32_t f32, const int32_t* block_table,
                          int32_t max_blocks, int32_t page_size, const int32_t* seg_start, const int32_t* seg_len,
                          const int32_t* seg_pos0, const int32_t* seg_slot, int32_t n_seg, int32_t max_q, int32_t H,
@@ -404,6 +439,9 @@ static int attn_any_impl(const void* q, const void* k_pool, const void* v_pool, 
                 "prl_attn_any: bad shape (H=%d G=%d dim=%d vdim=%d; dim <= 512, vdim <= 256)", H, G, dim, vdim);
   PRL_CHECK_ARG(window >= 0 && keep_first >= 0 && softcap >= 0.f, "prl_attn_any: bad mask (window=%d keep_first=%d)", window, keep_first);
   const int vr = (vdim + 31) / 32;
+  if (!f32 && g_attn_tensor_cores && max_q >= kMmaMinRows && attn_mma_fits(dim, vdim, q, k_pool, v_pool))
+    return attn_mma_launch(q, k_pool, v_pool, block_table, max_blocks, page_size, seg_start, seg_len, seg_pos0, seg_slot, n_seg,
+                           max_q, H, G, dim, scale, window, keep_first, softcap, out_is_t, out, (cudaStream_t)st);
   if (f32) return dispatch_attn<float>(vr, q, k_pool, v_pool, block_table, max_blocks, page_size, seg_start, seg_len, seg_pos0,
                                        seg_slot, n_seg, max_q, H, G, dim, vdim, scale, window, keep_first, softcap, out_is_t, out, (cudaStream_t)st);
   return dispatch_attn<__nv_bfloat16>(vr, q, k_pool, v_pool, block_table, max_blocks, page_size, seg_start, seg_len, seg_pos0,

@@ -178,6 +178,8 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const TA* __restrict__ A,
 // ---- bf16 tensor-core variant ------------------------------------------------------------------------------------------
 constexpr int kBN = 128, kBK = 32, kPad = 8;      // tile N, K step, padding (halves) that keeps ldmatrix conflict-free
 constexpr int kLds = kBK + kPad;                  // 40 halves = 80 bytes per staged row
+constexpr int kStages = 4;                        // cp.async stages in flight: a few-row tile is a pure weight stream
+constexpr size_t kMmaSmem = (size_t)kStages * (kTile + kBN) * kLds * sizeof(__nv_bfloat16);
 
 __device__ __forceinline__ void cp_async16_zfill(void* dst, const void* src, int bytes) {
   const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
@@ -202,8 +204,11 @@ __global__ void __launch_bounds__(256) moe_gemm_mma_kernel(const __nv_bfloat16* 
   pdl_wait();
   const int tile = blockIdx.y;
   if (tile >= meta[0]) return;
-  __shared__ __align__(16) __nv_bfloat16 As[2][kTile][kLds];
-  __shared__ __align__(16) __nv_bfloat16 Bs[2][kBN][kLds];
+  extern __shared__ __align__(16) unsigned char mma_smem[];
+  typedef __nv_bfloat16 (*ATile)[kTile][kLds];
+  typedef __nv_bfloat16 (*BTile)[kBN][kLds];
+  ATile As = reinterpret_cast<ATile>(mma_smem);                                           // [kStages][64][40]
+  BTile Bs = reinterpret_cast<BTile>(mma_smem + (size_t)kStages * kTile * kLds * sizeof(__nv_bfloat16));   // [kStages][128][40]
   __shared__ int32_t a_row[kTile], c_row[kTile];
   const int e = tiles[3 * tile], s0 = tiles[3 * tile + 1], M = tiles[3 * tile + 2];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -239,16 +244,15 @@ __global__ void __launch_bounds__(256) moe_gemm_mma_kernel(const __nv_bfloat16* 
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  stage(0, 0);
+  // kStages - 1 steps in flight; a commit per step keeps the group count regular (empty past the end, where `stage`
+  // copies nothing but zero fill into a buffer nobody reads)
+#pragma unroll
+  for (int st = 0; st < kStages - 1; ++st) stage(st * kBK, st);
   int buf = 0;
-  for (int k0 = 0; k0 < K; k0 += kBK, buf ^= 1) {
-    if (k0 + kBK < K) {
-      stage(k0 + kBK, buf ^ 1);
-      asm volatile("cp.async.wait_group 1;" ::: "memory");
-    } else {
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
-    }
-    __syncthreads();
+  for (int k0 = 0; k0 < K; k0 += kBK, buf = (buf + 1) % kStages) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(kStages - 2) : "memory");
+    __syncthreads();            // step k0 has landed for every thread, and every warp is done with the buffer refilled next
+    stage(k0 + (kStages - 1) * kBK, (buf + kStages - 1) % kStages);
 #pragma unroll
     for (int kk = 0; kk < kBK; kk += 16) {
       uint32_t af[2][4], bf[2][4];
@@ -261,8 +265,8 @@ __global__ void __launch_bounds__(256) moe_gemm_mma_kernel(const __nv_bfloat16* 
 #pragma unroll
         for (int j = 0; j < 4; ++j) mma_bf16(acc[i][j], af[i], bf[j >> 1][(j & 1) * 2], bf[j >> 1][(j & 1) * 2 + 1]);
     }
-    __syncthreads();
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
 #pragma unroll
   for (int i = 0; i < 2; ++i)
 #pragma unroll
@@ -326,7 +330,9 @@ extern "C" int prl_moe_gemm(const void* A, int32_t a_is_f32, int64_t lda, int32_
   if (!a_is_f32 && !w_is_f32 && K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 && expert_stride % 8 == 0 &&
       ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0) {
     dim3 grid_tc((unsigned)((N + kBN - 1) / kBN), (unsigned)max_tiles);
-    PRL_CUDA(launch_pdl(moe_gemm_mma_kernel, grid_tc, dim3(256), (size_t)0, s, (const bf16*)A, lda, a_mod, (const bf16*)W,
+    static SmemAttr attr = {};
+    PRL_CUDA(ensure_smem(moe_gemm_mma_kernel, (int)kMmaSmem, attr));
+    PRL_CUDA(launch_pdl(moe_gemm_mma_kernel, grid_tc, dim3(256), kMmaSmem, s, (const bf16*)A, lda, a_mod, (const bf16*)W,
                         expert_stride, ldw, perm, meta, tiles, (int)N, (int)K, C, ldc, c_perm));
     PRL_LAUNCH_CHECK();
     return PRL_OK;

@@ -277,6 +277,30 @@ def test_bf16_serving_mode(cuda_device, plain_gemm):
     assert bc.rel_err(bc.stream_logits(eng, toks, [100, 2, 30])[clear], ref[clear]) < BF16_TOL
 
 
+@pytest.mark.parametrize("dim,window,keep_first", [(64, 37, 1), (128, 64, 4), (32, 129, 70), (64, 0, 0)])
+def test_tensor_core_attention_for_prompt_portions(cuda_device, dim, window, keep_first):
+    """bf16 with head sizes 32 / 64 / 128: portions of 16 rows and more take the mma.sync attention kernel.  Peaked softmax,
+    330 tokens over five page borders, two query heads per key head; against the CUDA-core kernel on the same cache
+    (they differ only by the bf16 rounding of the softmax weights) and against the oracle."""
+    from pipelinerl_b200 import _lib
+    config = _peaked(window or 1000, keep_first, heads=4, kv_heads=2, dim=dim)
+    config["width"] = 64
+    wt = _only(_weights(config, 9), "right")
+    toks = bc.tokens_for(config, 330, seed=3)
+    ref = bc.oracle_logits(config, wt, toks)
+    eng = bc.build_engine(config, wt, torch.bfloat16, cuda_device)
+    lib = _lib.load()
+    try:
+        fast = [bc.stream_logits(eng, toks, portions) for portions in ([330], [63, 17, 16, 130, 65, 20])]
+        lib.prl_attn_any_tensor_cores(0)
+        plain = [bc.stream_logits(eng, toks, portions) for portions in ([330], [63, 17, 16, 130, 65, 20])]
+    finally:
+        lib.prl_attn_any_tensor_cores(1)
+    for f, p in zip(fast, plain):
+        assert bc.rel_err(f, p) < 0.25 * BF16_TOL
+        assert bc.rel_err(f, ref) < 2 * BF16_TOL and bc.rel_err(p, ref) < 2 * BF16_TOL
+
+
 def test_greedy_generation_through_the_scheduler(cuda_device):
     """add_request / run_prefill / CUDA-graph token steps / harvest, five prompts on two slots (slots and pages are
     reused), greedy ids against the oracle wherever its top-2 margin is not a rounding matter."""
