@@ -729,6 +729,10 @@ int prl_mlstm_out(const float* o_aug, int32_t n, int32_t H, int32_t dv, const fl
 int64_t prl_moe_max_tiles(int64_t pairs, int32_t experts);
 int prl_moe_route(const float* logits, int64_t ld, int32_t n, int32_t experts, int32_t top, int32_t softmax_weights,
                   int32_t* sel, float* wsel, int32_t* perm, int32_t* meta, int32_t* tiles, prl_stream_t stream);
+/* router product (fp32 sums in a fixed order), choice and grouping without the logits going through memory */
+int prl_moe_router(const void* x, int32_t x_is_f32, const void* Wr, int32_t w_is_f32, int32_t n, int32_t W, int32_t experts,
+                   int32_t top, int32_t softmax_weights, int32_t* sel, float* wsel, int32_t* perm, int32_t* meta,
+                   int32_t* tiles, prl_stream_t stream);
 int prl_moe_gemm(const void* A, int32_t a_is_f32, int64_t lda, int32_t a_mod, const void* W, int32_t w_is_f32,
                  int64_t expert_stride, int64_t ldw, const int32_t* perm, const int32_t* meta, const int32_t* tiles,
                  int64_t max_tiles, int64_t N, int64_t K, float* C, int64_t ldc, int32_t c_perm, prl_stream_t stream);

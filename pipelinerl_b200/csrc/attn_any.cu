@@ -279,12 +279,12 @@ __global__ void __launch_bounds__(kDecWarps * 32) attn_decode_any_kernel(
       const T* kr = k_pool + (((int64_t)bt[kt / page_size] * G + g) * page_size + kt % page_size) * dim;
       if (vec) {
         int d = 0;
-        for (; d + 4 * E <= dim; d += 4 * E) {              // four 16-byte loads in flight per lane
-          uint4 raw[4];
+        for (; d + 8 * E <= dim; d += 8 * E) {              // eight 16-byte loads in flight per lane
+          uint4 raw[8];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) raw[u] = *reinterpret_cast<const uint4*>(kr + d + u * E);
+          for (int u = 0; u < 8; ++u) raw[u] = *reinterpret_cast<const uint4*>(kr + d + u * E);
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
+          for (int u = 0; u < 8; ++u) {
             float kf[E];
             unpack16<T>(raw[u], kf);
 #pragma unroll
@@ -327,11 +327,12 @@ __global__ void __launch_bounds__(kDecWarps * 32) attn_decode_any_kernel(
       for (int i = 0; i < VR; ++i) acc[hh][i] *= corr;
     }
     const uint32_t seen_mask = __ballot_sync(0xffffffffu, seen);
-    for (int j0 = 0; j0 < kKeysPerTile; j0 += 4) {             // the loads of four keys in flight together
-      if (!(seen_mask >> j0 & 0xfu)) continue;                 // warp-uniform
-      float vv[4][VR];
+    constexpr int KB = VR <= 4 ? 8 : 4;                        // keys whose value loads are in flight together
+    for (int j0 = 0; j0 < kKeysPerTile; j0 += KB) {
+      if (!(seen_mask >> j0 & ((1u << KB) - 1u))) continue;    // warp-uniform
+      float vv[KB][VR];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < KB; ++u) {
         const int kj = k0 + j0 + u;
         const bool on = seen_mask >> (j0 + u) & 1u;            // hidden keys are not read: their weight is zero anyway
         const T* vr = v_pool + (((int64_t)bt[(on ? kj : k0) / page_size] * G + g) * page_size + (on ? kj : k0) % page_size) * vdim;
@@ -342,7 +343,7 @@ __global__ void __launch_bounds__(kDecWarps * 32) attn_decode_any_kernel(
         }
       }
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
+      for (int u = 0; u < KB; ++u)
 #pragma unroll
         for (int hh = 0; hh < kDecHeads; ++hh) {
           const float pj = __shfl_sync(0xffffffffu, p[hh], j0 + u);

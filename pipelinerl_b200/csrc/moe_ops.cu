@@ -69,6 +69,61 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int64_t ld, i
     for (int c = 0; c < top; ++c) wsel[(int64_t)c * n + t] /= denom;
 }
 
+// Router and choice in one kernel: logits[e] = x . Wr[e] in fp32 (block per row, the row staged in shared memory, warps
+// take experts in turn, a lane sums every 32nd channel, then the warp's shuffle tree: a fixed order), then the top-k
+// pass of moe_route_kernel over the logits in shared memory.
+template <typename TX, typename TW>
+__global__ void __launch_bounds__(256) moe_router_kernel(const TX* __restrict__ x, const TW* __restrict__ Wr, int n, int W, int E,
+                                                         int top, int softmax_weights, int32_t* __restrict__ sel,
+                                                         float* __restrict__ wsel) {
+  pdl_wait();
+  extern __shared__ float rsm[];       // [W] the row | [E] logits
+  float* xs = rsm;
+  float* z = rsm + W;
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) xs[c] = to_f32(x[(int64_t)t * W + c]);
+  __syncthreads();
+  for (int e = warp; e < E; e += nw) {
+    const TW* w = Wr + (int64_t)e * W;
+    float a = 0.f;
+#pragma unroll 8
+    for (int c = lane; c < W; c += 32) a = fmaf(xs[c], to_f32(w[c]), a);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+    if (lane == 0) z[e] = a;
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  uint32_t taken = 0;
+  float zsel_max = 0.f, denom = 0.f;
+  for (int c = 0; c < top; ++c) {
+    float best = -INFINITY;
+    int arg = 0x7fffffff;
+    for (int j = 0; j < kMaxPerLane; ++j) {
+      const int e = lane + 32 * j;
+      if (e >= E) break;
+      if (taken >> j & 1u) continue;
+      const float v = z[e];
+      if (v > best) { best = v; arg = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+      if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+    }
+    if ((arg & 31) == lane) taken |= 1u << (arg >> 5);
+    if (c == 0) zsel_max = best;
+    denom += expf(best - zsel_max);
+    if (lane == 0) {
+      sel[(int64_t)c * n + t] = arg;
+      wsel[(int64_t)c * n + t] = softmax_weights ? expf(best - zsel_max) : sigmoid_f(best);
+    }
+  }
+  if (softmax_weights && lane == 0)
+    for (int c = 0; c < top; ++c) wsel[(int64_t)c * n + t] /= denom;
+}
+
 // meta[0] = number of tiles; tiles[3 * i + {0, 1, 2}] = expert, first sorted place, rows
 __global__ void __launch_bounds__(1024) moe_group_kernel(const int32_t* __restrict__ sel, int pairs, int E,
                                                          int32_t* __restrict__ perm, int32_t* __restrict__ meta,
@@ -313,6 +368,35 @@ extern "C" int prl_moe_route(const float* logits, int64_t ld, int32_t n, int32_t
                 "prl_moe_route: bad shape (experts=%d top=%d; at most %d experts)", experts, top, 32 * kMaxPerLane);
   cudaStream_t s = (cudaStream_t)st;
   PRL_CUDA(launch_pdl(moe_route_kernel, dim3((n + 7) / 8), dim3(256), (size_t)0, s, logits, ld, n, experts, top, softmax_weights, sel, wsel));
+  PRL_LAUNCH_CHECK();
+  PRL_CUDA(launch_pdl(moe_group_kernel, dim3(1), dim3(1024), (size_t)(2 * experts * sizeof(int32_t)), s, (const int32_t*)sel, n * top, experts, perm, meta, tiles));
+  PRL_LAUNCH_CHECK();
+  return PRL_OK;
+}
+
+// Router product, choice and grouping in two launches: x [n, W] and the router matrix [experts, W] in fp32 or bf16.
+// Needs (W + experts) * 4 bytes of shared memory; returns PRL_ERR_INVALID beyond 160 KB (use prl_gemm_any + prl_moe_route).
+extern "C" int prl_moe_router(const void* x, int32_t x_is_f32, const void* Wr, int32_t w_is_f32, int32_t n, int32_t W,
+                              int32_t experts, int32_t top, int32_t softmax_weights, int32_t* sel, float* wsel, int32_t* perm,
+                              int32_t* meta, int32_t* tiles, prl_stream_t st) {
+  PRL_CHECK_ARG(x && Wr && sel && wsel && perm && meta && tiles, "prl_moe_router: NULL argument");
+  PRL_CHECK_ARG(n >= 1 && W >= 1 && experts >= 1 && experts <= 32 * kMaxPerLane && top >= 1 && top <= experts,
+                "prl_moe_router: bad shape (experts=%d top=%d; at most %d experts)", experts, top, 32 * kMaxPerLane);
+  const size_t smem = ((size_t)W + experts) * sizeof(float);
+  PRL_CHECK_ARG(smem <= 160 * 1024, "prl_moe_router: a row of %d channels does not fit in shared memory", W);
+  cudaStream_t s = (cudaStream_t)st;
+  static SmemAttr attr[4] = {};
+#define PRL_RT(TX, TW, I)                                                                                              \
+  do {                                                                                                                 \
+    if (smem > 48 * 1024) PRL_CUDA(ensure_smem(moe_router_kernel<TX, TW>, (int)smem, attr[I]));                        \
+    PRL_CUDA(launch_pdl((moe_router_kernel<TX, TW>), dim3(n), dim3(256), smem, s, (const TX*)x, (const TW*)Wr, n, W, experts, top, \
+                        softmax_weights, sel, wsel));                                                                  \
+  } while (0)
+  if (x_is_f32 && w_is_f32) PRL_RT(float, float, 0);
+  else if (x_is_f32) PRL_RT(float, bf16, 1);
+  else if (w_is_f32) PRL_RT(bf16, float, 2);
+  else PRL_RT(bf16, bf16, 3);
+#undef PRL_RT
   PRL_LAUNCH_CHECK();
   PRL_CUDA(launch_pdl(moe_group_kernel, dim3(1), dim3(1024), (size_t)(2 * experts * sizeof(int32_t)), s, (const int32_t*)sel, n * top, experts, perm, meta, tiles));
   PRL_LAUNCH_CHECK();

@@ -563,6 +563,7 @@ class HybridEngine(EngineCore):
         self.force_plain_gemm = False      # tests: route every GEMM through the CUDA-core kernel
         self.unfused_glu = False           # tests: gate_up GEMM + activation kernel instead of the GEMM's gated epilogue
         self.force_plain_attn = False      # tests: the any-geometry attention kernel also where the tcgen05 ones fit
+        self.unfused_router = False        # tests: router logits through the GEMM and a separate choice kernel
         # Long prompt portions run their recurrences as side-by-side pieces (prl_*_scan_split): same values up to fp32
         # rounding, many times the parallelism.  Off in the true-fp32 mode, whose results do not depend on the cut of
         # a prompt bit for bit.  A batch qualifies when its longest segment has split_min_rows rows.
@@ -855,10 +856,14 @@ class HybridEngine(EngineCore):
         two grouped GEMMs around the gated activation.  Returns [top][n][W] fp32 (R.moe_out), to be summed by the caller."""
         lib, st, W, f32 = self.lib, self._st, self.cfg.width, int(self.f32)
         pairs = n * e.top
-        _lib.check(lib.prl_gemm_any(R.xa.data_ptr(), f32, W, self.arena.ptr(w + "mlp.router"), f32, W, n, e.experts, W,
-                                    R.router.data_ptr(), e.experts, st))
-        _lib.check(lib.prl_moe_route(R.router.data_ptr(), e.experts, n, e.experts, e.top, 0, R.sel.data_ptr(),
-                                     R.wsel.data_ptr(), R.perm.data_ptr(), R.moe_meta.data_ptr(), R.moe_tiles.data_ptr(), st))
+        route = (R.sel.data_ptr(), R.wsel.data_ptr(), R.perm.data_ptr(), R.moe_meta.data_ptr(), R.moe_tiles.data_ptr(), st)
+        if (W + e.experts) * 4 <= 160 * 1024 and not self.unfused_router:
+            _lib.check(lib.prl_moe_router(R.xa.data_ptr(), f32, self.arena.ptr(w + "mlp.router"), f32, n, W, e.experts, e.top, 0,
+                                          *route))
+        else:
+            _lib.check(lib.prl_gemm_any(R.xa.data_ptr(), f32, W, self.arena.ptr(w + "mlp.router"), f32, W, n, e.experts, W,
+                                        R.router.data_ptr(), e.experts, st))
+            _lib.check(lib.prl_moe_route(R.router.data_ptr(), e.experts, n, e.experts, e.top, 0, *route))
         tiles = int(lib.prl_moe_max_tiles(pairs, e.experts))
         table = (R.perm.data_ptr(), R.moe_meta.data_ptr(), R.moe_tiles.data_ptr(), tiles)
         _lib.check(lib.prl_moe_gemm(R.xa.data_ptr(), f32, W, n, self.arena.ptr(w + "mlp.experts.gate_up"), f32,
