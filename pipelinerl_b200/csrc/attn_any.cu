@@ -210,7 +210,7 @@ int launch_attn(const void* q, const void* kp, const void* vp, const int32_t* bt
 // the kernel above.  Segments that are not exactly one row long are skipped (the host picks this kernel only when
 // every segment is one row, or empty).
 constexpr int kDecHeads = 4;
-constexpr int kDecWarps = 8;
+constexpr int kDecWarps = 16;
 
 template <typename T> struct Chunk;        // 16 bytes of cache elements
 template <> struct Chunk<float> { static constexpr int n = 4; };
