@@ -473,7 +473,8 @@ __global__ void act_store_kernel(const float* __restrict__ P, int64_t ld, int F,
 }
 
 // ---- matrix-memory LSTM (mLSTM) --------------------------------------------------------------------------------------
-// Gates of the stabilised recurrence, per head:  i = cap tanh((zi + bi) / cap),  f = logsigmoid(cap tanh((zf + bf) / cap)),
+// Gates of the stabilised recurrence, per head:  i = cap tanh((zi + bi) / cap),  f = logsigmoid(cap tanh((zf + bf) / cap))
+// (cap == 0: i = zi + bi, f = logsigmoid(zf + bf)),
 //   m_t = max(f + m_(t-1), i),   keep_t = exp(f + m_(t-1) - m_t),   take_t = exp(i - m_t)
 // so that S_t = keep_t S_(t-1) + take_t k v^T is what prl_decay_scan runs.  m is carried per sequence slot (0 at the
 // start); the walk over a segment's tokens is sequential, one warp per head: 32 tokens' transcendentals at a time in
@@ -499,8 +500,9 @@ __global__ void mlstm_gates_kernel(const float* __restrict__ P, int64_t ldp, int
       float gi = 0.f, gf = 0.f;
       if (t < len) {
         const float* pr = P + (row0 + t) * ldp;
-        gi = cap * tanhf((pr[off_i + h] + bias_i[h]) / cap);
-        gf = logsigmoid_g(cap * tanhf((pr[off_f + h] + bias_f[h]) / cap));
+        const float zi = pr[off_i + h] + bias_i[h], zf = pr[off_f + h] + bias_f[h];
+        gi = cap > 0.f ? cap * tanhf(zi / cap) : zi;              // cap == 0: the gates are not capped
+        gf = logsigmoid_g(cap > 0.f ? cap * tanhf(zf / cap) : zf);
       }
       float m_prev = 0.f, m_mine = 0.f;
       const int nt = min(32, len - t0);
@@ -769,7 +771,7 @@ extern "C" int prl_mlstm_gates(const float* P, int64_t ldp, int32_t off_i, int32
                                const int32_t* seg_slot, int32_t n_seg, float* m_state, float* gates, float* minv,
                                prl_stream_t st) {
   PRL_CHECK_ARG(P && bias_i && bias_f && seg_start && seg_len && seg_slot && m_state && gates && minv && H >= 1 && n_seg >= 1 &&
-                cap > 0.f, "prl_mlstm_gates: bad argument");
+                cap >= 0.f, "prl_mlstm_gates: bad argument");
   int th = 32 * H;
   th = th > 256 ? 256 : th;
   PRL_CUDA(launch_pdl(mlstm_gates_kernel, dim3(n_seg), dim3(th), (size_t)0, (cudaStream_t)st, P, ldp, off_i, off_f, bias_i, bias_f, cap, H, seg_start, seg_len, seg_slot, m_state, gates, minv));

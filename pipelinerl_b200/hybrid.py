@@ -222,14 +222,16 @@ class HybridConfig:
                     mlp = MlpSpec(ff=int(f["ff"]), limit=0.0, kind="relu2")
                 elif kind == "moe":
                     sh = f.get("shared")
+                    inf = float("inf")          # an expert without a limit is not clamped
                     moe = MoeSpec(int(f["router"]["experts"]), int(f["router"]["top"]), int(f["expert"]["ff"]),
-                                  float(f["expert"]["limit"]), int(sh["ff"]) if sh else 0, float(sh["limit"]) if sh else 0.0)
+                                  float(f["expert"].get("limit", inf)), int(sh["ff"]) if sh else 0,
+                                  float(sh.get("limit", inf)) if sh else 0.0)
                     mlp = MlpSpec(ff=moe.shared_ff, limit=moe.shared_limit, kind="moe", moe=moe)
                 else:
                     raise ValueError(f"layer {i}: unknown feed-forward kind {kind!r}")
             if L["type"] == "mlstm":
-                specs.append(dict(kind="mlstm", mlp=mlp, mlstm=MlstmSpec(int(m["heads"]), int(m["dim"]), int(m["vdim"]),
-                                                                         float(m["gate_cap"]))))
+                specs.append(dict(kind="mlstm", mlp=mlp, mlstm=MlstmSpec(int(m["heads"]), int(m["dim"]), int(m.get("vdim", m["dim"])),
+                                                                         float(m.get("gate_cap", 0.0)))))      # 0: gates not capped
             elif L["type"] == "parallel":
                 a, r = m["left"], m["right"]
                 mask = a.get("mask") or {}
@@ -237,7 +239,8 @@ class HybridConfig:
                                 0, 10000.0, float(a["scale"]), softcap=float(a.get("softcap", 0.0)),
                                 window=int(mask.get("size", 0)), keep_first=int(mask.get("keep_first", 0)), head_norm=True,
                                 bias=True, value_is_key=True, gate=False)
-                lin = LightningSpec(int(r["heads"]), int(r["dim"]), int(r["vdim"]), tuple(float(v) for v in r["decay"]))
+                decay = r["decay"] if isinstance(r["decay"], (list, tuple)) else [r["decay"]] * int(r["heads"])
+                lin = LightningSpec(int(r["heads"]), int(r["dim"]), int(r.get("vdim", r["dim"])), tuple(float(v) for v in decay))
                 specs.append(dict(kind="parallel_lin", mlp=mlp, attn=attn, lin=lin, left_scale=0.5, right_scale=0.5))
             else:
                 raise ValueError(f"layer {i}: unknown mixer type {L['type']!r}")
@@ -261,7 +264,7 @@ class HybridConfig:
     def validate(self) -> None:
         for i, L in enumerate(self.layers):
             if L.kind == "mlstm":
-                if L.mlstm.dim > 256 or L.mlstm.gate_cap <= 0:
+                if L.mlstm.dim > 256 or L.mlstm.gate_cap < 0:
                     raise ValueError(f"layer run {i}: bad matrix-memory geometry {L.mlstm}")
             elif L.kind == "parallel_lin":
                 a, r = L.attn, L.lin
